@@ -91,7 +91,8 @@ class GroupInfo:
 def group_needs(needs: Dict[int, object]) -> List[GroupInfo]:
     """{cache id -> need} -> groups, in order of first appearance."""
     groups: Dict[tuple, GroupInfo] = {}
-    for cid in sorted(needs):
+    # a cache id is a number, or (number, index) for a mixer that keeps several things
+    for cid in sorted(needs, key=lambda c: c if isinstance(c, tuple) else (c, -1)):
         need = needs[cid]
         if need is None:
             continue

@@ -45,7 +45,9 @@ def _ensure_builtin() -> None:
 
 def resolve_architecture(config_dict: Dict[str, Any]) -> Architecture:
     _ensure_builtin()
-    names = config_dict.get("architectures") or []
+    names = list(config_dict.get("architectures") or [])
+    if isinstance(config_dict.get("architecture"), str):         # some designs name themselves with one string
+        names.append(config_dict["architecture"])
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]

@@ -1,0 +1,167 @@
+// What lies between the q/k/v projection and the paged attention kernels for an attention whose queries and
+// keys are normalised over the whole projection, rotated by position (and whose values are rotated too), and
+// what lies behind them.  Everything here is computed in 32-bit from the projection's output and rounded once.
+//
+// tnx_rotary_qkv_prep, one thread block per token at position p:
+//   q <- q / sqrt(mean_all(q^2) + eps) * wq        (over all heads at once; skipped without wq)
+//   k <- k / sqrt(mean_all(k^2) + eps) * wk
+//   on the first `rot_dims` dims of each head of q and k, dim i paired with dim i + rot_dims/2:
+//       (u, v) <- (u cos a - v sin a, v cos a + u sin a),  a = p * inv_freq_qk[i]
+//   q of head h <- q * head_scale[h]                (skipped without head_scale)
+//   values, when inv_freq_v is given: over all v_dim dims, dim m paired with m + v_dim/2, a = p * inv_freq_v[m]
+//   q, k and v are written with `D` dims a head (D >= k_dim, v_dim; the rest zero), the layout the paged
+//   attention kernels take: zeros in q and k leave the scores alone, zeros in v give zero output columns.
+//
+// tnx_rotary_unrotate, one thread block per token at position p: each head's first v_dim output dims of the
+// attention (D a head) are turned back, pair m by -p * inv_freq_v[m], multiplied by out_scale and written
+// v_dim a head into a (possibly wider) activation buffer.
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void rotary_qkv_prep_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
+                                       const int* __restrict__ token_request, const int* __restrict__ positions,
+                                       const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                                       const float* __restrict__ head_scale, const float* __restrict__ inv_freq_qk,
+                                       int rot_dims, const float* __restrict__ inv_freq_v, T* __restrict__ q_out,
+                                       T* __restrict__ k_out, T* __restrict__ v_out, int H, int G, int dk, int dv, int D) {
+    extern __shared__ float sm[];                   // q [H * dk], k [G * dk], v [G * dv]
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n = blockIdx.x;
+    if (token_request[n] < 0) return;               // a padded row of a captured batch
+    const float pos = (float)positions[n];
+    const T* row = proj + (size_t)n * ld;
+    float* qs = sm;
+    float* ks = qs + H * dk;
+    float* vs = ks + G * dk;
+    const int nq = H * dk, nk = G * dk, nv = G * dv;
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < nq; c += blockDim.x) { const float v = to_float(row[q_off + c]); qs[c] = v; sq += v * v; }
+    for (int c = threadIdx.x; c < nk; c += blockDim.x) { const float v = to_float(row[k_off + c]); ks[c] = v; sk += v * v; }
+    for (int c = threadIdx.x; c < nv; c += blockDim.x) vs[c] = to_float(row[v_off + c]);
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);                    // block_sum synchronises: the rows are in shared memory now
+    const float rq = wq ? 1.0f / sqrtf(sq / (float)nq + eps) : 1.f;
+    const float rk = wk ? 1.0f / sqrtf(sk / (float)nk + eps) : 1.f;
+    const int half = rot_dims / 2;
+
+    // queries and keys: pairs of the rotated part, then the dims that pass unchanged, then the padding
+    for (int which = 0; which < 2; ++which) {
+        const int heads = which ? G : H;
+        const float* src = which ? ks : qs;
+        const float* w = which ? wk : wq;
+        const float rinv = which ? rk : rq;
+        T* dst = (which ? k_out : q_out) + (size_t)n * heads * D;
+        for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
+            const int h = e / half, i = e % half;
+            const int c0 = h * dk + i, c1 = c0 + half;
+            float u = src[c0] * rinv, v = src[c1] * rinv;
+            if (w) { u *= w[c0]; v *= w[c1]; }
+            float sn, cs;
+            sincosf(pos * inv_freq_qk[i], &sn, &cs);
+            float a = u * cs - v * sn, b = v * cs + u * sn;
+            if (!which && head_scale) { a *= head_scale[h]; b *= head_scale[h]; }
+            dst[h * D + i] = from_float<T>(a);
+            dst[h * D + i + half] = from_float<T>(b);
+        }
+        const int rest = D - rot_dims;
+        for (int e = threadIdx.x; e < heads * rest; e += blockDim.x) {
+            const int h = e / rest, c = rot_dims + e % rest;
+            float y = 0.f;
+            if (c < dk) {
+                y = src[h * dk + c] * rinv;
+                if (w) y *= w[h * dk + c];
+                if (!which && head_scale) y *= head_scale[h];
+            }
+            dst[h * D + c] = from_float<T>(y);
+        }
+    }
+    // values
+    T* vd = v_out + (size_t)n * G * D;
+    if (inv_freq_v) {
+        const int hv = dv / 2;
+        for (int e = threadIdx.x; e < G * hv; e += blockDim.x) {
+            const int h = e / hv, m = e % hv;
+            const float u = vs[h * dv + m], v = vs[h * dv + m + hv];
+            float sn, cs;
+            sincosf(pos * inv_freq_v[m], &sn, &cs);
+            vd[h * D + m] = from_float<T>(u * cs - v * sn);
+            vd[h * D + m + hv] = from_float<T>(v * cs + u * sn);
+        }
+    } else {
+        for (int e = threadIdx.x; e < nv; e += blockDim.x) vd[(e / dv) * D + e % dv] = from_float<T>(vs[e]);
+    }
+    const int vrest = D - dv;
+    for (int e = threadIdx.x; e < G * vrest; e += blockDim.x) vd[(e / vrest) * D + dv + e % vrest] = from_float<T>(0.f);
+}
+
+template <typename T>
+__global__ void rotary_unrotate_kernel(const T* __restrict__ att, const int* __restrict__ token_request,
+                                       const int* __restrict__ positions, const float* __restrict__ inv_freq_v,
+                                       float out_scale, T* __restrict__ out, int out_ld, int H, int dv, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n = blockIdx.x;
+    if (token_request[n] < 0) return;
+    const float pos = (float)positions[n];
+    const T* src = att + (size_t)n * H * D;
+    T* dst = out + (size_t)n * out_ld;
+    if (inv_freq_v) {
+        const int hv = dv / 2;
+        for (int e = threadIdx.x; e < H * hv; e += blockDim.x) {
+            const int h = e / hv, m = e % hv;
+            const float u = to_float(src[h * D + m]), v = to_float(src[h * D + m + hv]);
+            float sn, cs;
+            sincosf(pos * inv_freq_v[m], &sn, &cs);                 // the turn by -a: (u cos a + v sin a, v cos a - u sin a)
+            dst[h * dv + m] = from_float<T>((u * cs + v * sn) * out_scale);
+            dst[h * dv + m + hv] = from_float<T>((v * cs - u * sn) * out_scale);
+        }
+    } else {
+        for (int e = threadIdx.x; e < H * dv; e += blockDim.x)
+            dst[e] = from_float<T>(to_float(src[(e / dv) * D + e % dv]) * out_scale);
+    }
+}
+
+}  // namespace
+
+TNX_EXPORT int tnx_rotary_qkv_prep(const void* proj, int ld, int q_off, int k_off, int v_off, const int* token_request,
+                                   const int* positions, const float* wq, const float* wk, float eps,
+                                   const float* head_scale, const float* inv_freq_qk, int rot_dims,
+                                   const float* inv_freq_v, void* q_out, void* k_out, void* v_out, int n_tokens, int H,
+                                   int G, int dk, int dv, int D, int is_h16, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || D < dk || D < dv || rot_dims < 0 || rot_dims > dk || rot_dims % 2 ||
+        (rot_dims && !inv_freq_qk) || (inv_freq_v && dv % 2))
+        return TNX_ERR_BAD_ARG;
+    const size_t smem = (size_t)(H * dk + G * dk + G * dv) * sizeof(float);
+    if (smem > 200 * 1024) return TNX_ERR_UNSUPPORTED;
+    const int threads = 256;
+#define PREP_LAUNCH(T)                                                                                                  \
+    do {                                                                                                                \
+        if (smem + 1024 > 48 * 1024)                                                                                    \
+            cudaFuncSetAttribute(rotary_qkv_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+        return tnx_launch_in_order(rotary_qkv_prep_kernel<T>, dim3(n_tokens), dim3(threads), smem, stream,              \
+                                   (const T*)proj, ld, q_off, k_off, v_off, token_request, positions, wq, wk, eps,      \
+                                   head_scale, inv_freq_qk, rot_dims, inv_freq_v, (T*)q_out, (T*)k_out, (T*)v_out, H,   \
+                                   G, dk, dv, D);                                                                       \
+    } while (0)
+    if (is_h16) PREP_LAUNCH(h16);
+    PREP_LAUNCH(float);
+#undef PREP_LAUNCH
+}
+
+TNX_EXPORT int tnx_rotary_unrotate(const void* att, const int* token_request, const int* positions,
+                                   const float* inv_freq_v, float out_scale, void* out, int out_ld, int n_tokens, int H,
+                                   int dv, int D, int is_h16, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (H <= 0 || dv <= 0 || D < dv || (inv_freq_v && dv % 2) || out_ld < H * dv) return TNX_ERR_BAD_ARG;
+    const int threads = H * dv >= 2048 ? 256 : 128;
+    if (is_h16)
+        return tnx_launch_in_order(rotary_unrotate_kernel<h16>, dim3(n_tokens), dim3(threads), 0, stream, (const h16*)att,
+                                   token_request, positions, inv_freq_v, out_scale, (h16*)out, out_ld, H, dv, D);
+    return tnx_launch_in_order(rotary_unrotate_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)att,
+                               token_request, positions, inv_freq_v, out_scale, (float*)out, out_ld, H, dv, D);
+}

@@ -43,6 +43,11 @@ SOURCES: Dict[str, str] = {
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
+    "rmsnorm": "rmsnorm.cu",
+    "rotary_qkv": "rotary_qkv.cu",
+    "retention": "retention.cu",
+    "mingru": "mingru.cu",
+    "gated_act": "gated_act.cu",
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

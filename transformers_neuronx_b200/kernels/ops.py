@@ -755,3 +755,195 @@ def attention(ctx, group, q, cache, out, n_heads, scale, window=0, new_kv=None):
         kv_append(new_kv[0], new_kv[1], new_kv[2], cache, ctx.page_size)
     attention_simt(q, cache, ctx.block_tables[group], ctx.token_request, ctx.positions, out, n_heads, scale,
                    window)
+
+
+# ---------------------------------------------------------------------------------------------
+# RMS norm, rotations by position, recurrent mixers, the gated feed-forward's elementwise step.
+def _f32_vec(t, name, n=None):
+    if t is None:
+        return
+    _need(t, name, torch.float32, 1)
+    if n is not None and t.shape[0] != n:
+        raise KernelError(f"{name} has {t.shape[0]} elements, expected {n}")
+
+
+def rms_norm(x, weight, eps, out_f32=None, out_act=None, rows=None, x_scale=1.0, delta=None, weight_offset=0.0):
+    """Rows of y = x_scale * x + delta (delta optional, 32-bit like x) divided by their root mean square
+    (eps inside the root) and multiplied by (weight + weight_offset) when a weight is given.  out_f32 may
+    be x itself.  `rows` (int32) picks input rows."""
+    lib = _lib("rmsnorm", out_act)
+    _need(x, "x", torch.float32, 2)
+    H = x.shape[1]
+    n_rows = rows.shape[0] if rows is not None else x.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+    if delta is not None:
+        _need(delta, "delta", torch.float32, 2)
+        if tuple(delta.shape) != tuple(x.shape):
+            raise KernelError("delta must have the shape of x")
+    _f32_vec(weight, "weight", H)
+    for t, nm in ((out_f32, "out_f32"), (out_act, "out_act")):
+        if t is not None:
+            _need(t, nm, torch.float32 if nm == "out_f32" else _FLOATS, 2)
+            if t.shape[0] < n_rows or t.shape[1] != H:
+                raise KernelError(f"{nm} has shape {tuple(t.shape)}, needs [{n_rows}, {H}]")
+    _check(lib.tnx_rms_norm(_p(x), c_float(x_scale), _p(delta), _p(rows), _p(weight), c_float(weight_offset),
+                            c_float(eps), _p(out_f32), _p(out_act), c_int(n_rows), c_int(H),
+                            c_int(_is_h16(out_act) if out_act is not None else 0), _stream()), "rms_norm")
+
+
+def rotary_qkv_prep(proj, q_off, k_off, v_off, token_request, positions, q_weight, k_weight, eps, head_scale,
+                    inv_freq_qk, rot_dims, inv_freq_v, q_out, k_out, v_out, n_heads, n_kv_heads, k_dim, v_dim, pad_dim):
+    """From one product's output `proj` [N, *] (queries at column q_off, keys at k_off, values at v_off): the
+    queries and keys normalised over the whole projection (where a weight is given), rotated by position
+    on their first rot_dims dims, the queries multiplied by their head's number; the values rotated over
+    all their dims (where inv_freq_v is given); each written with pad_dim dims a head, the rest zero."""
+    lib = _lib("rotary_qkv", proj, q_out)
+    _need(proj, "proj", _FLOATS, None, contiguous=False)
+    N, width, ld = _rows_2d(proj, "proj")
+    H, G, dk, dv, D = n_heads, n_kv_heads, k_dim, v_dim, pad_dim
+    if max(q_off + H * dk, k_off + G * dk, v_off + G * dv) > width:
+        raise KernelError("the projection is narrower than its q/k/v columns")
+    for t, nm, w in ((q_out, "q_out", H * D), (k_out, "k_out", G * D), (v_out, "v_out", G * D)):
+        _need(t, nm, proj.dtype, 2)
+        if tuple(t.shape) != (N, w):
+            raise KernelError(f"{nm} must be [{N}, {w}]")
+    _f32_vec(q_weight, "q_weight", H * dk); _f32_vec(k_weight, "k_weight", G * dk); _f32_vec(head_scale, "head_scale", H)
+    _f32_vec(inv_freq_qk, "inv_freq_qk", rot_dims // 2 if rot_dims else None); _f32_vec(inv_freq_v, "inv_freq_v", dv // 2)
+    _need(token_request, "token_request", torch.int32, 1)
+    _need(positions, "positions", torch.int32, 1)
+    _check(lib.tnx_rotary_qkv_prep(_p(proj), c_int(ld), c_int(q_off), c_int(k_off), c_int(v_off), _p(token_request),
+                                   _p(positions), _p(q_weight), _p(k_weight), c_float(eps), _p(head_scale),
+                                   _p(inv_freq_qk), c_int(rot_dims), _p(inv_freq_v), _p(q_out), _p(k_out), _p(v_out),
+                                   c_int(N), c_int(H), c_int(G), c_int(dk), c_int(dv), c_int(D), c_int(_is_h16(proj)),
+                                   _stream()), "rotary_qkv_prep")
+
+
+def rotary_unrotate(att, token_request, positions, inv_freq_v, out_scale, out, n_heads, v_dim, pad_dim):
+    """att [N, n_heads * pad_dim]: each head's first v_dim dims turned back by the token's position (pair m with
+    m + v_dim/2, by -p * inv_freq_v[m]; no turn without inv_freq_v), times out_scale, written v_dim a head into
+    `out` [N, n_heads * v_dim] (a column slice of a wider buffer is allowed)."""
+    lib = _lib("rotary_qkv", att, out)
+    _need(att, "att", _FLOATS, 2)
+    N = att.shape[0]
+    if att.shape[1] != n_heads * pad_dim:
+        raise KernelError("att must hold pad_dim dims a head")
+    _need(out, "out", att.dtype, None, contiguous=False)
+    No, wo, out_ld = _rows_2d(out, "out")
+    if (No, wo) != (N, n_heads * v_dim):
+        raise KernelError(f"out must be [{N}, {n_heads * v_dim}]")
+    _f32_vec(inv_freq_v, "inv_freq_v", v_dim // 2)
+    _check(lib.tnx_rotary_unrotate(_p(att), _p(token_request), _p(positions), _p(inv_freq_v), c_float(out_scale),
+                                   _p(out), c_int(out_ld), c_int(N), c_int(n_heads), c_int(v_dim), c_int(pad_dim),
+                                   c_int(_is_h16(att)), _stream()), "rotary_unrotate")
+
+
+def retention_prep(proj, q_off, k_off, token_request, positions, inv_freq, rot_dims, k_scale, q_out, k_out, n_heads, k_dim):
+    """32-bit queries and keys [N, n_heads * k_dim] for the retention scan: rotated by position on their first
+    rot_dims dims, the keys then multiplied by k_scale."""
+    lib = _lib("retention", proj)
+    _need(proj, "proj", _FLOATS, None, contiguous=False)
+    N, width, ld = _rows_2d(proj, "proj")
+    if max(q_off, k_off) + n_heads * k_dim > width:
+        raise KernelError("the projection is narrower than its q/k columns")
+    for t, nm in ((q_out, "q_out"), (k_out, "k_out")):
+        _need(t, nm, torch.float32, 2)
+        if tuple(t.shape) != (N, n_heads * k_dim):
+            raise KernelError(f"{nm} must be [{N}, {n_heads * k_dim}]")
+    _f32_vec(inv_freq, "inv_freq", rot_dims // 2 if rot_dims else None)
+    _check(lib.tnx_retention_prep(_p(proj), c_int(ld), c_int(q_off), c_int(k_off), _p(token_request), _p(positions),
+                                  _p(inv_freq), c_int(rot_dims), c_float(k_scale), _p(q_out), _p(k_out), c_int(N),
+                                  c_int(n_heads), c_int(k_dim), c_int(_is_h16(proj)), _stream()), "retention_prep")
+
+
+def retention_scan(q, k, v, decay, state, q_start, q_len, state_slots, out, n_heads, k_dim, v_dim):
+    """S <- decay S + k v^T, o = S^T q, token by token for every request of the step (q_start, q_len: its rows;
+    q_len 0 or slot < 0: skipped).  q, k: 32-bit [N, n_heads * k_dim]; v: [N, n_heads * v_dim] view in the
+    activation type or 32-bit; state: 32-bit [slots, n_heads, v_dim, k_dim]; out: 32-bit [N, n_heads * v_dim]."""
+    lib = _lib("retention", v)
+    N = q.shape[0]
+    for t, nm in ((q, "q"), (k, "k")):
+        _need(t, nm, torch.float32, 2)
+        if tuple(t.shape) != (N, n_heads * k_dim):
+            raise KernelError(f"{nm} must be [{N}, {n_heads * k_dim}]")
+    _need(v, "v", _FLOATS, None, contiguous=False)
+    Nv, wv, v_ld = _rows_2d(v, "v")
+    if (Nv, wv) != (N, n_heads * v_dim):
+        raise KernelError(f"v must be [{N}, {n_heads * v_dim}]")
+    _need(state, "state", torch.float32, 4)
+    if tuple(state.shape[1:]) != (n_heads, v_dim, k_dim):
+        raise KernelError(f"state must be [slots, {n_heads}, {v_dim}, {k_dim}]")
+    _need(out, "out", torch.float32, 2)
+    if tuple(out.shape) != (N, n_heads * v_dim):
+        raise KernelError(f"out must be [{N}, {n_heads * v_dim}]")
+    _f32_vec(decay, "decay", n_heads)
+    for t, nm in ((q_start, "q_start"), (q_len, "q_len"), (state_slots, "state_slots")):
+        _need(t, nm, torch.int32, 1)
+    R = q_len.shape[0]
+    if q_start.shape[0] < R or state_slots.shape[0] < R:
+        raise KernelError("q_start and state_slots must cover every request of q_len")
+    _check(lib.tnx_retention_scan(_p(q), _p(k), _p(v), c_int(v_ld), _p(decay), _p(state), _p(q_start), _p(q_len),
+                                  _p(state_slots), _p(out), c_int(R), c_int(n_heads), c_int(k_dim), c_int(v_dim),
+                                  c_int(_is_h16(v)), _stream()), "retention_scan")
+
+
+def headwise_gated_rms_norm(o, gate, token_request, weight, eps, out_scale, out, n_heads, v_dim):
+    """out = o / rms(o over each head's v_dim dims) (* weight) * silu(gate) * out_scale; o 32-bit [N, n_heads * v_dim],
+    gate (optional) and out views in the activation type."""
+    lib = _lib("retention", gate, out)
+    _need(o, "o", torch.float32, 2)
+    N = o.shape[0]
+    if o.shape[1] != n_heads * v_dim:
+        raise KernelError(f"o must be [{N}, {n_heads * v_dim}]")
+    gate_ld = 0
+    if gate is not None:
+        _need(gate, "gate", out.dtype, None, contiguous=False)
+        Ng, wg, gate_ld = _rows_2d(gate, "gate")
+        if (Ng, wg) != (N, n_heads * v_dim):
+            raise KernelError(f"gate must be [{N}, {n_heads * v_dim}]")
+    _need(out, "out", _FLOATS, None, contiguous=False)
+    No, wo, out_ld = _rows_2d(out, "out")
+    if (No, wo) != (N, n_heads * v_dim):
+        raise KernelError(f"out must be [{N}, {n_heads * v_dim}]")
+    _f32_vec(weight, "weight", v_dim)
+    _check(lib.tnx_headwise_gated_rms_norm(_p(o), _p(gate), c_int(gate_ld), _p(token_request), _p(weight), c_float(eps),
+                                           c_float(out_scale), _p(out), c_int(out_ld), c_int(N), c_int(n_heads),
+                                           c_int(v_dim), c_int(_is_h16(out)), _stream()), "headwise_gated_rms_norm")
+
+
+def mingru_scan(proj, z_off, x_off, g_off, state, q_start, q_len, state_slots, out, width, out_scale=1.0):
+    """The minGRU recurrence over every request's rows of the step, from the raw projections in `proj` [N, *]
+    (update gate at column z_off, candidate at x_off, output gate at g_off or None); state 32-bit [slots, width];
+    out [N, width] in proj's type: the new state times silu(output gate) times out_scale."""
+    lib = _lib("mingru", proj, out)
+    _need(proj, "proj", _FLOATS, None, contiguous=False)
+    N, wide, ld = _rows_2d(proj, "proj")
+    offs = [z_off, x_off] + ([g_off] if g_off is not None else [])
+    if max(offs) + width > wide or min(offs) < 0:
+        raise KernelError("the projection is narrower than its gate columns")
+    _need(state, "state", torch.float32, 2)
+    if state.shape[1] != width:
+        raise KernelError(f"state must be [slots, {width}]")
+    _need(out, "out", proj.dtype, None, contiguous=False)
+    No, wo, out_ld = _rows_2d(out, "out")
+    if (No, wo) != (N, width):
+        raise KernelError(f"out must be [{N}, {width}]")
+    for t, nm in ((q_start, "q_start"), (q_len, "q_len"), (state_slots, "state_slots")):
+        _need(t, nm, torch.int32, 1)
+    R = q_len.shape[0]
+    _check(lib.tnx_mingru_scan(_p(proj), c_int(ld), c_int(z_off), c_int(x_off), c_int(-1 if g_off is None else g_off),
+                               _p(state), _p(q_start), _p(q_len), _p(state_slots), _p(out), c_int(out_ld), c_float(out_scale),
+                               c_int(R), c_int(width), c_int(_is_h16(proj)), _stream()), "mingru_scan")
+
+
+def gated_activation(gate_up, out, activation):
+    """out = act(gate_up[:, :F]) * gate_up[:, F:], F = out's width."""
+    lib = _lib("gated_act", gate_up, out)
+    _need(gate_up, "gate_up", _FLOATS, None, contiguous=False)
+    N, wide, ld = _rows_2d(gate_up, "gate_up")
+    _need(out, "out", gate_up.dtype, None, contiguous=False)
+    No, F, out_ld = _rows_2d(out, "out")
+    if No != N or wide != 2 * F:
+        raise KernelError(f"gate_up must be [{No}, {2 * F}]")
+    _check(lib.tnx_gated_activation(_p(gate_up), c_int(ld), _p(out), c_int(out_ld), c_int(N), c_int(F),
+                                    c_int(activation_code(activation)), c_int(_is_h16(out)), _stream()), "gated_activation")

@@ -1,2 +1,3 @@
 from .decoder import DecoderModel
 from . import opt  # noqa: F401  registers OPTForCausalLM; another built-in architecture is one more line here
+from . import vononex  # noqa: F401  registers Vononex

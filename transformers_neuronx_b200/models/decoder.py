@@ -22,7 +22,7 @@ class DecoderModel:
         for ls in spec.layers:
             self.blocks.append(build_block(ls.block, build_part("norm", ls.norm1), build_part("mixer", ls.mixer),
                                            build_part("norm", ls.norm2),
-                                           build_part("feed_forward", ls.feed_forward)))
+                                           build_part("feed_forward", ls.feed_forward), layer_spec=ls))
         self.head = Head(spec.head)
         for e in spec.schedule:
             if not (0 <= e.layer < len(self.blocks)):
@@ -83,10 +83,14 @@ class DecoderModel:
         needs: Dict[int, object] = {}
         for e in self.spec.schedule:
             need = self.blocks[e.layer].mixer.cache_need()
-            if e.cache in needs and needs[e.cache] != need:
-                raise ValueError(f"cache {e.cache} is shared by mixers with different needs: "
-                                 f"{needs[e.cache]} and {need}")
-            needs[e.cache] = need
+            # a mixer that keeps several things (say pages of keys and values and a recurrent state) returns a
+            # tuple of needs: they become the caches (entry's cache, 0), (entry's cache, 1), ...
+            several = isinstance(need, (tuple, list))
+            for j, nd in enumerate(need if several else (need,)):
+                cid = (e.cache, j) if several else e.cache
+                if cid in needs and needs[cid] != nd:
+                    raise ValueError(f"cache {cid} is shared by mixers with different needs: {needs[cid]} and {nd}")
+                needs[cid] = nd
         return needs
 
     def load(self, tensors: Dict[str, torch.Tensor], device, act_dtype) -> None:

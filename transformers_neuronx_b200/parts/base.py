@@ -80,11 +80,12 @@ class StepContext:
         self._scratch_used = {}
 
     # what the mixer of the running schedule entry owns
-    def cache(self) -> torch.Tensor:
-        return self.storage.tensor(self.cache_id)
+    def cache(self, sub=None) -> torch.Tensor:
+        """The cache of the running entry's mixer; `sub`: which one, for a mixer whose cache_need() is a tuple."""
+        return self.storage.tensor(self.cache_id if sub is None else (self.cache_id, sub))
 
-    def cache_group(self) -> int:
-        return self.storage.group_of(self.cache_id)
+    def cache_group(self, sub=None) -> int:
+        return self.storage.group_of(self.cache_id if sub is None else (self.cache_id, sub))
 
 
 class Part:
@@ -135,6 +136,7 @@ class NormedInput:
 
 class Mixer(Part):
     takes_normed_input = False      # True: forward's `h` may be a NormedInput (the part hands it to a Linear)
+    can_overwrite = False           # True: forward(ctx, h, out, accumulate=False) writes its result instead of adding it
 
     def cache_need(self):
         return None
@@ -145,6 +147,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     takes_normed_input = False
+    can_overwrite = False
 
     def forward(self, ctx, h, residual):
         raise NotImplementedError

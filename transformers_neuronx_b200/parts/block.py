@@ -4,6 +4,11 @@ pre_norm  (src/transformers_neuronx/opt/model.py:336-376):  x += mixer(norm1(x))
 post_norm (the reference rejects it, opt/config.py:23-24; this is the usual order):
                                                           x = norm1(x + mixer(x)); x = norm2(x + ff(x))
 
+post_norm_scaled:                                         x = norm1(a x + mixer(x)); x = norm2(a x + ff(x))
+    with a = the layer's residual_scale; a layer may have no feed-forward (then no second norm).  The
+    sublayer's result goes into a 32-bit buffer of its own and the norm's kernel forms the sum
+    (Norm.forward_sum), so the stream is read and written once per sublayer.
+
 `x` is the 32-bit residual stream and is updated in place; `x_act` is its copy in the activation
 type, which a block that feeds x itself into a matrix product needs on entry
 (``needs_act_input``) and keeps current (``keeps_act_current``).
@@ -58,5 +63,40 @@ class PostNormBlock:
         self.norm2.forward(ctx, x, out_f32=x, out_act=x_act)
 
 
+class ScaledPostNormBlock:
+    """x <- norm(residual_scale * x + sublayer(x)).  A sublayer that can write its result instead of adding it
+    (``can_overwrite``: forward(ctx, h, out, accumulate=False)) is asked to; any other adds into a zeroed buffer."""
+    needs_act_input = True
+    keeps_act_current = True
+    takes_layer_spec = True
+
+    def __init__(self, norm1, mixer, norm2, feed_forward, layer_spec=None):
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        self.residual_scale = float(getattr(layer_spec, "residual_scale", 1.0))
+        for n in (norm1, norm2 if feed_forward is not None else None):
+            if n is not None and not hasattr(n, "forward_sum"):
+                raise ValueError(f"a post_norm_scaled block needs norms that normalise a sum; {type(n).__name__} does not")
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    @staticmethod
+    def _run(ctx, part, h, out):
+        if getattr(part, "can_overwrite", False):
+            part.forward(ctx, h, out, accumulate=False)
+        else:
+            out.zero_()
+            part.forward(ctx, h, out)
+
+    def forward(self, ctx, x, x_act):
+        out = ctx.scratch(x.shape[0], x.shape[1], x.dtype)
+        self._run(ctx, self.mixer, x_act, out)
+        self.norm1.forward_sum(ctx, x, self.residual_scale, out, out_f32=x, out_act=x_act)
+        if self.feed_forward is not None:
+            self._run(ctx, self.feed_forward, x_act, out)
+            self.norm2.forward_sum(ctx, x, self.residual_scale, out, out_f32=x, out_act=x_act)
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("post_norm_scaled", ScaledPostNormBlock)
 register_block("post_norm", PostNormBlock)

@@ -87,7 +87,9 @@ class Head(Part):
     @property
     def libraries(self):
         libs = ["layernorm", "gemm_simt", "gemm_tc", "gemv"]
-        return tuple(libs)
+        if self.final_norm is not None:
+            libs += list(self.final_norm.libraries)
+        return tuple(dict.fromkeys(libs))
 
     def tensor_specs(self):
         s = self.spec

@@ -3,11 +3,12 @@
 (hlo.py:485-501).  The activation and the residual add run in the epilogues of the two products."""
 from __future__ import annotations
 
+from ..kernels import ops
 from ..kernels.ops import activation_code
 from .base import FeedForward
-from .linear import Linear
+from .linear import Linear, fuse_linears
 from .registry import register_feed_forward
-from .spec import DenseFeedForwardSpec
+from .spec import DenseFeedForwardSpec, GatedFeedForwardSpec
 
 
 class DenseFeedForward(FeedForward):
@@ -36,4 +37,42 @@ class DenseFeedForward(FeedForward):
         self.fc2.forward(a, residual, residual=residual)
 
 
+class GatedDenseFeedForward(FeedForward):
+    """down(act(gate(h)) * up(h)), all three with optional biases: gate and up are one product, the
+    activation and the multiplication one elementwise kernel in 32-bit on its output."""
+    graph_safe = True
+    can_overwrite = True
+    libraries = ("gemm_simt", "gemm_tc", "gemv", "gated_act")
+
+    def __init__(self, spec: GatedFeedForwardSpec):
+        self.spec = spec
+        activation_code(spec.activation)
+        if spec.gate.out_features != spec.up.out_features or spec.down.in_features != spec.up.out_features:
+            raise ValueError("gate, up and down of a gated feed-forward must agree on the inner width")
+        self.gate, self.up, self.down = Linear(spec.gate), Linear(spec.up), Linear(spec.down)
+        self.gate_up = None
+
+    def tensor_specs(self):
+        return self.gate.tensor_specs() + self.up.tensor_specs() + self.down.tensor_specs()
+
+    def load(self, tensors, device, act_dtype):
+        for p in (self.gate, self.up, self.down):
+            p.load(tensors, device, act_dtype)
+        self.gate_up = fuse_linears([self.gate, self.up], device)
+        for p in (self.gate, self.up):
+            p.weight = p.bias = None
+
+    def parameter_bytes(self):
+        return self.gate_up.parameter_bytes() + self.down.parameter_bytes()
+
+    def forward(self, ctx, h, out, accumulate=True):
+        N, F = h.shape[0], self.spec.up.out_features
+        gu = ctx.scratch(N, 2 * F)
+        self.gate_up.forward(h, gu)
+        a = ctx.scratch(N, F)
+        ops.gated_activation(gu, a, self.spec.activation)
+        self.down.forward(a, out, residual=out if accumulate else None)
+
+
 register_feed_forward("dense", DenseFeedForward)
+register_feed_forward("gated_dense", GatedDenseFeedForward)

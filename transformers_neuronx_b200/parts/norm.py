@@ -1,4 +1,9 @@
-"""LayerNorm as the reference computes it: statistics and affine in 32-bit over the hidden axis
+"""Norms over the hidden axis.
+
+RMS norm: y / sqrt(mean(y^2) + eps) * (weight + weight_offset), in 32-bit; it can normalise a sum
+y = x_scale * x + delta in the same kernel, which is what a post-norm block with a scaled residual asks for.
+
+LayerNorm as the reference computes it: statistics and affine in 32-bit over the hidden axis
 (src/transformers_neuronx/hlo.py:84-105), with eps, scale and shift as parameters of the part."""
 from __future__ import annotations
 
@@ -43,4 +48,36 @@ class LayerNorm(Norm):
         ops.layer_norm(x, self.weight, self.bias, self.spec.eps, out_f32=out_f32, out_act=out_act, rows=rows)
 
 
+class RMSNorm(Norm):
+    graph_safe = True
+    libraries = ("rmsnorm",)
+
+    def __init__(self, spec: NormSpec):
+        if spec.bias:
+            raise ValueError("an RMS norm has no shift")
+        self.spec = spec
+        self.weight = None
+
+    def tensor_specs(self):
+        s = self.spec
+        return [TensorSpec(s.weight, (s.size,), "norm_weight")] if s.weight else []
+
+    def load(self, tensors, device, act_dtype):
+        s = self.spec
+        self.weight = to_device(tensors[s.weight], device, torch.float32) if s.weight else None
+
+    def parameter_bytes(self):
+        return self.weight.numel() * 4 if self.weight is not None else 0
+
+    def forward(self, ctx, x, out_f32=None, out_act=None, rows=None):
+        ops.rms_norm(x, self.weight, self.spec.eps, out_f32=out_f32, out_act=out_act, rows=rows,
+                     weight_offset=self.spec.weight_offset)
+
+    def forward_sum(self, ctx, x, x_scale, delta, out_f32=None, out_act=None):
+        """norm(x_scale * x + delta) in one kernel; out_f32 may be x."""
+        ops.rms_norm(x, self.weight, self.spec.eps, out_f32=out_f32, out_act=out_act, x_scale=x_scale, delta=delta,
+                     weight_offset=self.spec.weight_offset)
+
+
 register_norm("layer_norm", LayerNorm)
+register_norm("rms_norm", RMSNorm)

@@ -39,5 +39,10 @@ def build_part(family: str, spec):
     return _lookup(family, spec.kind)(spec)
 
 
-def build_block(kind: str, norm1, mixer, norm2, feed_forward):
-    return _lookup("block", kind)(norm1, mixer, norm2, feed_forward)
+def build_block(kind: str, norm1, mixer, norm2, feed_forward, layer_spec=None):
+    """A block class that sets ``takes_layer_spec`` also receives the layer's spec (for constants of the
+    arrangement itself, such as a scale of the residual)."""
+    cls = _lookup("block", kind)
+    if getattr(cls, "takes_layer_spec", False):
+        return cls(norm1, mixer, norm2, feed_forward, layer_spec=layer_spec)
+    return cls(norm1, mixer, norm2, feed_forward)

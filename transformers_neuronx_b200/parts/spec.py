@@ -22,11 +22,20 @@ class LinearSpec:
 
 @dataclass(frozen=True)
 class NormSpec:
-    kind: str                        # 'layer_norm'
+    kind: str                        # 'layer_norm' | 'rms_norm'
     size: int
     eps: float
     weight: Optional[str] = None     # None: no elementwise scale
     bias: Optional[str] = None
+    weight_offset: float = 0.0       # 'rms_norm': the scale is weight + weight_offset (1.0: "one plus" weights)
+
+
+@dataclass(frozen=True)
+class RotarySpec:
+    """Rotation of pairs of dims by position: over the first `dims` dims of a head, dim i is paired with
+    dim i + dims/2 and turned by position * base^(-2i/dims)."""
+    dims: int
+    base: float
 
 
 @dataclass(frozen=True)
@@ -56,6 +65,80 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class RotaryAttentionSpec:
+    """Softmax attention over the paged cache whose queries and keys may be normalised over the whole
+    projection, are rotated by position, and whose score is multiplied by a number per head; the values
+    may be rotated as well (and each head's output turned back by the query's position)."""
+    kind: str                        # 'rotary_attention'
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    k_dim: int                       # per-head size of queries and keys
+    v_dim: int                       # per-head size of values
+    scale: float
+    q: LinearSpec = None
+    k: LinearSpec = None
+    v: LinearSpec = None
+    out: LinearSpec = None
+    rotary: Optional[RotarySpec] = None
+    rotate_values: bool = False      # values turned by their position over all v_dim dims (base of `rotary`)
+    q_norm: Optional[str] = None     # tensor [n_heads * k_dim]: RMS norm over the whole projection, before rotation
+    k_norm: Optional[str] = None     # tensor [n_kv_heads * k_dim]
+    norm_eps: float = 1e-6
+    head_scale: Optional[str] = None  # tensor [n_heads]: the score of head h is multiplied by its entry
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with a fixed decay per head: S <- decay S + k v^T, o = S^T q; each head's o divided by
+    its root mean square, gated by silu of a projection, then the output projection."""
+    kind: str                        # 'retention'
+    hidden: int
+    n_heads: int
+    k_dim: int
+    v_dim: int
+    decay: Tuple[float, ...] = ()    # one per head
+    q: LinearSpec = None
+    k: LinearSpec = None
+    v: LinearSpec = None
+    gate: Optional[LinearSpec] = None
+    out: LinearSpec = None
+    rotary: Optional[RotarySpec] = None
+    k_scale: float = 1.0             # keys are multiplied by it after rotation
+    norm_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Several mixers side by side on the same input; the result is the sum of scale_i * branch_i."""
+    kind: str                        # 'parallel'
+    branches: Tuple[Any, ...] = ()
+    scales: Tuple[float, ...] = ()
+
+
+@dataclass(frozen=True)
+class MinGRUSpec:
+    """S <- (1 - z) S + z cand with gates that read the current token only; output W_o (S * silu(gate))."""
+    kind: str                        # 'mingru'
+    hidden: int
+    width: int
+    z: LinearSpec = None             # update gate (sigmoid)
+    x: LinearSpec = None             # candidate
+    gate: Optional[LinearSpec] = None
+    out: LinearSpec = None
+
+
+@dataclass(frozen=True)
+class GatedFeedForwardSpec:
+    kind: str                        # 'gated_dense'
+    gate: LinearSpec = None
+    up: LinearSpec = None
+    down: LinearSpec = None
+    activation: str = "silu"         # applied to the gate's product
+
+
+@dataclass(frozen=True)
 class DenseFeedForwardSpec:
     kind: str                        # 'dense'
     fc1: LinearSpec = None
@@ -65,11 +148,12 @@ class DenseFeedForwardSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    block: str                       # 'pre_norm' | 'post_norm' | a registered kind
+    block: str                       # 'pre_norm' | 'post_norm' | 'post_norm_scaled' | a registered kind
     norm1: Any = None
     mixer: Any = None
     norm2: Any = None
-    feed_forward: Any = None
+    feed_forward: Any = None         # None: the layer has no feed-forward (and no second norm)
+    residual_scale: float = 1.0      # 'post_norm_scaled': x <- norm(residual_scale * x + sublayer(x))
 
 
 @dataclass(frozen=True)
