@@ -296,3 +296,38 @@ def test_greedy_generation_through_the_engine(dtype):
                 assert float(lg.max() - lg[tok]) / float(lg.abs().max()) <= 2 * TOLERANCE[dtype], (i, tok)
     eng.runner.cache.check()
     assert eng.runner.cache.slots.num_free == 3
+
+
+def test_the_entry_point_class_and_the_command_line(tmp_path):
+    """config.json picks the entry-point class; greedy `sample` equals the plain argmax, teacher-forced; the demo
+    command line writes a folder of random weights from a config.json and samples from it."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from transformers_neuronx_b200 import NeuronAutoModelForCausalLM, VononexForSampling
+    m = _model("P")
+    model = NeuronAutoModelForCausalLM.from_pretrained(m.folder, batch_size=2, amp="f32", n_positions=64)
+    assert isinstance(model, VononexForSampling)
+    model.to_neuron()
+    prompts = torch.tensor([m.random_ids(9, 41), m.random_ids(9, 42)])
+    seq = model.sample(prompts, sequence_length=20, top_k=1)
+    assert tuple(seq.shape) == (2, 20) and torch.equal(seq[:, :9], prompts)
+    for row in seq.tolist():
+        logits = m.plain_logits(row)
+        for i in range(9, 20):
+            lg = logits[i - 1]
+            if row[i] != int(lg.argmax()):
+                assert float(lg.max() - lg[row[i]]) / float(lg.abs().max()) <= 1e-4
+                break
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    demo = os.path.join(root, "bin", "vononex_demo")
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(CONFIG_P))
+    folder = tmp_path / "model"
+    r = subprocess.run([sys.executable, demo, "--amp", "bf16", "save", str(folder), "--random", "--config", str(cfg)],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([sys.executable, demo, "--amp", "bf16", "run", str(folder), "--batch_size", "2", "--n_positions", "24",
+                        "--top_k", "1"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "generated_sequence=" in r.stdout, r.stderr

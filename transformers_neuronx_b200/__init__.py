@@ -1,4 +1,4 @@
-"""A one-GPU inference engine for the OPT decoder on NVIDIA B200 (sm_100a): typed configuration,
+"""A one-GPU inference engine for the OPT decoder (and the Vononex decoder) on NVIDIA B200 (sm_100a): typed configuration,
 weights by name, layers put together from parts, a paged cache, one step function, a scheduler,
 sampling, and hand-written CUDA kernels.  Capabilities follow aws-neuron/transformers-neuronx's OPT
 support; the design does not."""
@@ -7,7 +7,7 @@ __version__ = "0.1.0"
 from .config.generation_config import (BlkSparseAttnConfig, ContinuousBatchingConfig, GenerationConfig, NeuronConfig,
                                        SlidingWindowAttnConfig, SparseAttnConfig)      # as `from transformers_neuronx import ...`
 
-_LAZY = {"OPTForSampling": ".opt.model", "OPTForGreedySearch": ".opt.model",
+_LAZY = {"OPTForSampling": ".opt.model", "OPTForGreedySearch": ".opt.model", "VononexForSampling": ".vononex.model",
          "NeuronAutoModelForCausalLM": ".modeling_auto", "HuggingFaceGenerationModelAdapter": ".generation_utils"}
 
 

@@ -115,6 +115,12 @@ class VononexConfig:
     def vocab_size(self) -> int:
         return self.vocab
 
+    torch_dtype = "bfloat16"                 # the type the design's checkpoints are stored in
+
+    @property
+    def max_position_embeddings(self) -> int:
+        return self.max_positions
+
     eos_token_id: Optional[int] = None
     bos_token_id: Optional[int] = None
     pad_token_id: Optional[int] = None

@@ -1,7 +1,7 @@
 """The entry-point class of a model folder, chosen by its config.json.
 
 The reference maps `model_type` to one of its sampling classes
-(src/transformers_neuronx/modeling_auto.py:5-47).  Here the table holds OPT; another architecture
+(src/transformers_neuronx/modeling_auto.py:5-47).  Here the table holds OPT and Vononex; another architecture
 registers its own entry-point class beside its registration in config/registry.py.
 """
 from __future__ import annotations
@@ -20,6 +20,10 @@ def register_model_class(model_type: str, cls: type) -> None:
     NEURON_MODEL_FOR_CAUSAL_LM_MAPPING[model_type] = cls
 
 
+def _ensure_builtin() -> None:
+    from .vononex import model as _vononex  # noqa: F401  registers VononexForSampling
+
+
 class NeuronAutoModelForCausalLM:
     @classmethod
     def from_pretrained(cls, pretrained_model_name_or_path, *model_args, **kwargs):
@@ -27,6 +31,7 @@ class NeuronAutoModelForCausalLM:
             raise FileNotFoundError(f"{pretrained_model_name_or_path!r} is not a folder; there is no network here to "
                                     "fetch a model by name")
         arch, _ = load_config(pretrained_model_name_or_path)          # raises for an architecture nobody registered
+        _ensure_builtin()
         if arch.model_type not in NEURON_MODEL_FOR_CAUSAL_LM_MAPPING:
             raise AssertionError(f"The configuration model type '{arch.model_type}' has no entry-point class here "
                                  f"(known: {sorted(NEURON_MODEL_FOR_CAUSAL_LM_MAPPING)})")

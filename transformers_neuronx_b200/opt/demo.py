@@ -28,7 +28,6 @@ import torch
 from ..config import config_from_dict, load_config
 from ..models.decoder import DecoderModel
 from ..weights import load_tensors, save_safetensors, write_model_folder
-from .model import OPTForSampling
 
 PROMPT_TEXT = "Hello, I'm a language model,"
 
@@ -102,7 +101,8 @@ def _tokenizer(folder):
 
 def run(args):
     torch.manual_seed(15213)
-    print("running OPTForSampling.from_pretrained")
+    from ..modeling_auto import NeuronAutoModelForCausalLM      # the entry-point class is chosen by config.json
+    print("running NeuronAutoModelForCausalLM.from_pretrained")
     neuron_config = None
     if args.sparse_attn:                                    # gpt_demo.py:107-123
         if args.sparse_attn != "window":
@@ -110,7 +110,7 @@ def run(args):
         from ..config import NeuronConfig, SlidingWindowAttnConfig, SparseAttnConfig
         neuron_config = NeuronConfig(sparse_attn=SparseAttnConfig(
             attn_type="window", causal=True, sparse_attn_config=SlidingWindowAttnConfig(window_size=args.window_size)))
-    model = OPTForSampling.from_pretrained(args.load, batch_size=args.batch_size, amp=args.amp,
+    model = NeuronAutoModelForCausalLM.from_pretrained(args.load, batch_size=args.batch_size, amp=args.amp,
                                            n_positions=args.n_positions, neuron_config=neuron_config)
     print("running model.to_neuron")
     model.to_neuron()
@@ -121,7 +121,7 @@ def run(args):
         ids = tok.encode(PROMPT_TEXT)
     else:
         v = model.config.vocab_size
-        ids = [model.config.bos_token_id] + [3 + (7 * i) % (v - 3) for i in range(1, 9)]
+        ids = [model.config.bos_token_id or 0] + [3 + (7 * i) % (v - 3) for i in range(1, 9)]
     input_ids = torch.as_tensor([ids] * args.batch_size)
     if args.print_latency:
         runner = model.engine.runner

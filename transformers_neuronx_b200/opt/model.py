@@ -30,6 +30,8 @@ from ..kernels import ops
 
 
 class OPTForSampling:
+    ARCHITECTURE = "OPTForCausalLM"      # the registered architecture this entry point serves (a subclass names its own)
+
     def __init__(self, folder: str, config: OPTConfig, batch_size=1, amp=None, tp_degree=None, n_positions=2048,
                  unroll=None, context_length_estimate=None, context_unroll=None, neuron_config=None, **kwargs):
         for name, val in (("tp_degree", tp_degree), ("unroll", unroll), ("context_unroll", context_unroll),
@@ -42,13 +44,14 @@ class OPTForSampling:
         if kwargs:
             raise KeyError(f"unknown argument(s): {sorted(kwargs)}")
         if amp is None:                  # the checkpoint's own type (opt/model.py:38-41, dtypes.py:29-35)
-            amp = {"float16": "f16", "bfloat16": "bf16"}.get(str(config.torch_dtype).replace("torch.", ""), "f32")
+            amp = {"float16": "f16", "bfloat16": "bf16"}.get(str(getattr(config, "torch_dtype", None)).replace("torch.", ""), "f32")
         self.amp = amp
         self.dtype = canonical_dtype(amp)
         max_bucket = max(n_positions) if isinstance(n_positions, (list, tuple)) else n_positions
-        if max_bucket > config.max_position_embeddings:     # opt/model.py:51-57
+        longest = getattr(config, "max_position_embeddings", None) or getattr(config, "max_positions", None)
+        if longest is not None and max_bucket > longest:     # opt/model.py:51-57
             raise ValueError(f"Sequence length ({max_bucket}) cannot be larger than position embedding's "
-                             f"context size ({config.max_position_embeddings})!")
+                             f"context size ({longest})!")
         self.folder = folder
         self.config = config
         self.batch_size = max(batch_size) if isinstance(batch_size, (list, tuple)) else int(batch_size)
@@ -67,8 +70,8 @@ class OPTForSampling:
             raise FileNotFoundError(f"{pretrained_model_path!r} is not a folder; there is no network here to "
                                     "fetch a model by name")
         arch, config = load_config(pretrained_model_path)
-        if arch.name != "OPTForCausalLM":
-            raise ValueError(f"{pretrained_model_path} holds a {arch.name}, not an OPT model")
+        if arch.name != cls.ARCHITECTURE:
+            raise ValueError(f"{pretrained_model_path} holds a {arch.name}, not a {cls.ARCHITECTURE} model")
         return cls(pretrained_model_path, config, *model_args, **kwargs)
 
     def to_neuron(self):
@@ -135,7 +138,7 @@ class OPTForSampling:
         runner = self.engine.runner
         n_prompt = max(1, min(64, self.n_positions // 2))
         n_decode = max(0, min(8, self.n_positions - n_prompt - 1))
-        ids = [[self.config.bos_token_id] + [3 + (7 * i + b) % (self.config.vocab_size - 3) for i in range(1, n_prompt)]
+        ids = [[self.config.bos_token_id or 0] + [3 + (7 * i + b) % (self.config.vocab_size - 3) for i in range(1, n_prompt)]
                for b in range(self.batch_size)]
         graphs, runner.use_cuda_graphs = runner.use_cuda_graphs, False
         try:
