@@ -363,9 +363,138 @@ def workload_sweep(steps, warmup):
     return rows
 
 
-def extra_workload(name, steps, warmup, sizes=None):
+# ---- the Vononex decoder beside OPT at equal sizes ---------------------------------------------------
+# Layer sizes that resemble real models: width, attention heads (of 128 dims) on a quarter as many key/value
+# heads, retention heads of 128 x 128, a gated feed-forward of 8/3 the width (the parameters of OPT's 4x one),
+# a minGRU of 1.5x the width.
+VONONEX_SIZES = {"2048": dict(width=2048, heads=16, kv=4, ff=5504, gru=3072),
+                 "4096": dict(width=4096, heads=32, kv=8, ff=11008, gru=6144)}
+VONONEX_LAYERS = ("parallel", "mingru", "parallel", "parallel")
+
+
+def vononex_config(size):
+    z = VONONEX_SIZES[size]
+    rot = {"dims": 128, "base": 10000.0}
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": z["ff"]},
+           "mixer": {"left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": rot},
+                     "right": {"heads": z["heads"], "dim": 128, "vdim": 128, "rot": rot,
+                               "decay": [1.0 - 2.0 ** (-5 - 7 * h / z["heads"]) for h in range(z["heads"])]},
+                     "left_scale": 1.0, "right_scale": 1.0}}
+    gru = {"type": "mingru", "mlp": {"kind": "dense", "ff": z["ff"]}, "mixer": {"width": z["gru"]}}
+    return {"architecture": "Vononex", "vocab": 50272, "width": z["width"], "postln_alpha": 2.0, "norm": {"eps": 1e-5},
+            "init_std": 0.02, "max_positions": CONTEXT, "layers": [par if t == "parallel" else gru for t in VONONEX_LAYERS]}
+
+
+def build_vononex(size, dtype="bfloat16"):
+    import torch
+    from transformers_neuronx_b200.config import config_from_dict
+    from transformers_neuronx_b200.engine import build_model
+    from transformers_neuronx_b200.models.decoder import DecoderModel
+    arch, cfg = config_from_dict(vononex_config(size))
+    spec = arch.build_spec(cfg)
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(0)
+    tensors = {}
+    for s in DecoderModel(spec).tensor_specs():
+        t = torch.randn(s.shape, generator=g, device=dev, dtype=torch.float32) * cfg.init_std
+        tensors[s.name] = (1.0 + t) if s.kind == "norm_weight" else t.to(getattr(torch, dtype))
+    return build_model(spec, tensors, dtype, verbose=False), cfg
+
+
+def step_bytes(model, batch, ctx, tables_bytes):
+    """Bytes one decode step has to move: every weight once (of the embedding table only the batch's rows), the
+    live requests' pages, and every recurrent state read and written."""
+    n = model.parameter_bytes() - tables_bytes
+    for need in model.cache_needs().values():
+        if hasattr(need, "bytes_per_page"):
+            n += batch * ctx * need.bytes_per_page(16, model.act_dtype) // 16
+        elif need is not None:
+            k = 1
+            for d in need.shape:
+                k *= d
+            n += 2 * batch * k * 4
+    return n
+
+
+def profile_families(model, cfg, batch, prompt_tokens):
+    """ms per kernel family of one decode step at `batch` (context ending at CONTEXT) and of one prompt of
+    `prompt_tokens`, with CUDA events around every kernel call (graphs off; the families' sum is more than the
+    step's own time, where kernels overlap)."""
+    import torch
+    from transformers_neuronx_b200.engine import StepEntry, StepRunner
+    from transformers_neuronx_b200.kernels.profile import kernel_profile
+    out = {}
+    runner = StepRunner(model, 16, batch * CONTEXT // 16 + prompt_tokens // 16 + 1, batch + 1, CONTEXT, use_cuda_graphs=False)
+    for b in range(batch):
+        runner.add_request(b)
+        runner.cache.append(b, CONTEXT - 8)
+    dec = [StepEntry(b, [5 + b], [0]) for b in range(batch)]
+    runner.add_request("p")
+    pre = [StepEntry("p", [7] * prompt_tokens, [prompt_tokens - 1])]
+    for name, entries in (("decode", dec), ("prefill", pre)):
+        for rep in range(3):
+            if rep == 2:
+                with kernel_profile() as prof:
+                    runner.step(entries)
+                    out[name] = {k: [round(ms, 4), n] for k, (ms, n) in prof.totals().items()}
+            else:
+                runner.step(entries)
+            if name == "prefill":
+                runner.finish("p")
+                runner.add_request("p")
+    del runner
+    torch.cuda.empty_cache()
+    return out
+
+
+def workload_vononex(steps, warmup, sizes=None, only=None, batch=8):
+    """Prefill (one 2,048-token prompt) and decode (batch 1, 8, 64, contexts ending at 2,048) of a four-layer
+    Vononex decoder, and of a four-layer OPT decoder of the same width and heads, in bfloat16 with random
+    weights; per layer, with the decode step's share of the memory roofline and every kernel family's time."""
+    import torch
+    global DTYPE
+    DTYPE = "bfloat16"
+    hbm_gbs, tflops, peak_src = peaks()
+    rows = {"peaks": peak_src, "layers": list(VONONEX_LAYERS)}
+    if only is not None:                       # one part of one size alone (for profiling a small case)
+        model, cfg = build_vononex((sizes or ["2048"])[0])
+        if only == "decode":
+            ms, launches, _, _ = time_decode(model, cfg, batch, steps, warmup)
+            return {"only": only, "batch": batch, "ms_per_step": round(ms, 4), "launches": launches}
+        return {"only": only, "tokens": PREFILL_TOKENS, "ms": round(time_prefill(model, cfg, steps, warmup), 4)}
+    for size in (sizes or sorted(VONONEX_SIZES)):
+        z = VONONEX_SIZES[size]
+        opt_cfg = dict(OPT_6_7B, hidden_size=z["width"], num_attention_heads=z["heads"], ffn_dim=4 * z["width"],
+                       word_embed_proj_dim=z["width"])
+        for which in ("vononex", "opt"):
+            if which == "vononex":
+                model, cfg = build_vononex(size)
+                tables = cfg.vocab * cfg.width * 2                    # the embedding table: rows of the batch only
+            else:
+                model, cfg = build(len(VONONEX_LAYERS), dtype="bfloat16", base=opt_cfg)
+                tables = (cfg.max_position_embeddings + 2) * cfg.hidden_size * 2      # the output matrix is the token table
+            row = {"weights_gb": round(model.parameter_bytes() / 1e9, 3)}
+            pf = time_prefill(model, cfg, max(3, min(steps, 5)), 3)
+            row["prefill_ms"] = round(pf, 3)
+            row["prefill_tokens_per_s"] = round(PREFILL_TOKENS / (pf / 1e3), 1)
+            for b in (1, 8, 64):
+                ms, launches, _, _ = time_decode(model, cfg, b, steps, warmup)
+                row[f"decode_b{b}_ms"] = round(ms, 4)
+                row[f"decode_b{b}_tokens_per_s"] = round(b / (ms / 1e3), 1)
+                row[f"decode_b{b}_frac"] = round(step_bytes(model, b, CONTEXT - steps / 2, tables) / (ms / 1e3) / 1e9 / hbm_gbs, 4)
+                row[f"decode_b{b}_launches_per_step"] = launches // steps
+            row["families"] = profile_families(model, cfg, 8, PREFILL_TOKENS)
+            rows[f"{which}_{size}"] = row
+            del model
+            torch.cuda.empty_cache()
+    return rows
+
+
+def extra_workload(name, steps, warmup, sizes=None, only=None, batch=8):
     """One of the further workloads alone, printed as one JSON line of its own."""
-    if name == "family":
+    if name == "vononex":
+        res = workload_vononex(steps, warmup, sizes, only, batch)
+    elif name == "family":
         res = workload_family(steps, warmup, sizes)
     elif name == "sweep":
         res = workload_sweep(steps, warmup)
@@ -400,9 +529,10 @@ def main():
     ap.add_argument("--skip-large", action="store_true", help="leave out the OPT-13B and OPT-30B workloads")
     ap.add_argument("--dtype", default="float16", choices=["float16", "bfloat16"],
                     help="the serving type (float16 is what OPT checkpoints are stored in)")
-    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b", "family", "sweep"],
+    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b", "family", "sweep", "vononex"],
                     help="run one of the further workloads instead of the default line")
-    ap.add_argument("--sizes", default=None, help="for --workload family: comma-separated sizes (default: all of 125m .. 66b)")
+    ap.add_argument("--sizes", default=None, help="for --workload family: comma-separated sizes (default: all of 125m .. 66b); for --workload vononex: "
+                    "widths (2048, 4096)")
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
                     help="run just this part and print its time (for profiling a small case)")
     a = ap.parse_args()
@@ -415,7 +545,7 @@ def main():
     global DTYPE
     DTYPE = a.dtype
     if a.workload:
-        return extra_workload(a.workload, a.steps, a.warmup, a.sizes.split(",") if a.sizes else None)
+        return extra_workload(a.workload, a.steps, a.warmup, a.sizes.split(",") if a.sizes else None, a.only, a.batch)
     import torch
     hbm_gbs, tflops, peak_src = peaks()
     model, cfg = build(a.layers)

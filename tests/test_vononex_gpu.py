@@ -141,7 +141,7 @@ def test_headwise_norm_with_its_gate():
 def test_mingru_scan_carries_its_state_across_cuts():
     from transformers_neuronx_b200.kernels import ops
     g = torch.Generator().manual_seed(6)
-    T, W = 41, 33
+    T, W = 200, 33
     proj = torch.randn(T, 3 * W + 2, generator=g) * 2
     z, u, gt = (proj[:, 2 + i * W:2 + (i + 1) * W].double() for i in range(3))
     zz, cand = torch.sigmoid(z), torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
@@ -151,7 +151,7 @@ def test_mingru_scan_carries_its_state_across_cuts():
         want.append(S * VP.silu(gt[t]) * 0.7)
     state = torch.zeros(3, W, device=DEV)
     got, at = [], 0
-    for n in (1, 2, 9, 1, 4, 24):
+    for n in (1, 2, 9, 1, 4, 24, 70, 89):           # the long portions are spread over several warps
         out = torch.zeros(n, W, device=DEV)
         ops.mingru_scan(proj[at:at + n].to(DEV), 2, 2 + W, 2 + 2 * W, state, _i32([0, 0]), _i32([0, n]), _i32([0, 2]),
                         out, W, out_scale=0.7)

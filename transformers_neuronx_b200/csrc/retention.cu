@@ -26,6 +26,7 @@ __global__ void retention_prep_kernel(const T* __restrict__ proj, int ld, int q_
                                       const int* __restrict__ token_request, const int* __restrict__ positions,
                                       const float* __restrict__ inv_freq, int rot_dims, float k_scale,
                                       float* __restrict__ q_out, float* __restrict__ k_out, int H, int dk) {
+    extern __shared__ float sm[];                   // cos and sin of the token's angles, the same for every head
     pdl_launch_dependents();
     pdl_wait();
     const int n = blockIdx.x;
@@ -33,13 +34,16 @@ __global__ void retention_prep_kernel(const T* __restrict__ proj, int ld, int q_
     const float pos = (float)positions[n];
     const T* row = proj + (size_t)n * ld;
     const int half = rot_dims / 2;
+    float* cst = sm;
+    float* snt = sm + half;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &snt[i], &cst[i]);
+    __syncthreads();
     float* qd = q_out + (size_t)n * H * dk;
     float* kd = k_out + (size_t)n * H * dk;
     for (int e = threadIdx.x; e < H * half; e += blockDim.x) {
         const int h = e / half, i = e % half;
         const int c0 = h * dk + i, c1 = c0 + half;
-        float sn, cs;
-        sincosf(pos * inv_freq[i], &sn, &cs);
+        const float sn = snt[i], cs = cst[i];
         const float qu = to_float(row[q_off + c0]), qv = to_float(row[q_off + c1]);
         const float ku = to_float(row[k_off + c0]), kv = to_float(row[k_off + c1]);
         qd[c0] = qu * cs - qv * sn;
@@ -55,18 +59,33 @@ __global__ void retention_prep_kernel(const T* __restrict__ proj, int ld, int q_
     }
 }
 
-constexpr int SCAN_TOKENS = 8;        // tokens whose queries and keys are staged in shared memory at a time
+constexpr int SCAN_TOKENS_MOST = 32;  // most tokens whose queries and keys are staged in shared memory at a time
+constexpr int SCAN_STAGES = 2;        // one stage is computed on while the next one arrives
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // KPT: rows of a column one thread keeps; R: lanes a column's rows are spread over (KPT * R >= k_dim).
-// VEC: a thread's rows come in runs of four (rows 4 (r + R m) .. + 3), read as one 16-byte piece.
+// VEC: k_dim is a multiple of four: a thread's rows come in runs of four (rows 4 (r + R m) .. + 3), read as one
+// 16-byte piece, and the stages are filled with 16-byte asynchronous copies; otherwise with plain loads.
+// The R partial sums of an output are not added with shuffles token by token (a chain of round trips that the few
+// warps of a block cannot hide): every thread leaves its partial sum in shared memory, and after a stage's tokens
+// the block adds them up and stores the outputs.
+// A stage holds q [ST][DKP], k [ST][DKP] (columns from k_dim on stay zero) and v [ST][C], ST = stage_tokens: 32 for
+// portions of prompts, as few as one for a step of single tokens (less shared memory, more blocks an SM).
 template <typename T, int KPT, int R, bool VEC>
 __global__ void __launch_bounds__(256)
 retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr, const T* __restrict__ v, int v_ld,
                       const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ q_start,
                       const int* __restrict__ q_len, const int* __restrict__ state_slots, float* __restrict__ out,
-                      int H, int dk, int dv, int C) {
+                      int H, int dk, int dv, int C, int stage_tokens) {
     constexpr int DKP = KPT * R;
-    extern __shared__ __align__(16) float sm[];       // q [SCAN_TOKENS][DKP], k [SCAN_TOKENS][DKP], v [SCAN_TOKENS][C]
+    const int SCAN_TOKENS = stage_tokens;
+    extern __shared__ __align__(16) float sm[];
     pdl_launch_dependents();
     pdl_wait();
     const int req = blockIdx.z, h = blockIdx.y;
@@ -75,69 +94,237 @@ retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr
     const int slot = state_slots[req];
     if (slot < 0) return;
     const int t_first = q_start[req];
-    float* qs = sm;
-    float* ks = qs + SCAN_TOKENS * DKP;
-    float* vs = ks + SCAN_TOKENS * DKP;
+    const int stage_floats = SCAN_TOKENS * (2 * DKP + C);
+    float* part = sm + SCAN_STAGES * stage_floats;    // [SCAN_TOKENS][C * R] partial sums of the stage being computed
     const int jl = threadIdx.x / R, r = threadIdx.x % R;
     const int j = blockIdx.x * C + jl;
     const bool col = j < dv;
     const float dec = decay[h];
     float* st = state + (((size_t)slot * H + h) * dv + (col ? j : 0)) * dk;
 
-    float S[KPT];
-#pragma unroll
-    for (int m = 0; m < KPT; ++m) {
-        const int i = VEC ? 4 * (r + R * (m / 4)) + (m % 4) : r + R * m;
-        S[m] = (col && i < dk) ? st[i] : 0.f;
-    }
-    for (int t0 = 0; t0 < len; t0 += SCAN_TOKENS) {
+    // Fills stage `s` with the tokens from t0 on: queries and keys by asynchronous copies (VEC) or plain loads,
+    // values by plain loads (they change type on the way).
+    auto fill = [&](int s, int t0) {
+        float* qs = sm + s * stage_floats;
+        float* ks = qs + SCAN_TOKENS * DKP;
+        float* vs = ks + SCAN_TOKENS * DKP;
         const int nt = min(SCAN_TOKENS, len - t0);
-        __syncthreads();
-        for (int e = threadIdx.x; e < nt * DKP; e += blockDim.x) {
-            const int tt = e / DKP, i = e % DKP;
-            const size_t g = (size_t)(t_first + t0 + tt) * H * dk + (size_t)h * dk + i;
-            qs[e] = i < dk ? qr[g] : 0.f;
-            ks[e] = i < dk ? kr[g] : 0.f;
+        const size_t g0 = (size_t)(t_first + t0) * H * dk + (size_t)h * dk;
+        if (VEC) {
+            const int pieces = dk / 4;
+            for (int e = threadIdx.x; e < nt * pieces; e += blockDim.x) {
+                const int tt = e / pieces, c = e % pieces;
+                cp_async_16(qs + tt * DKP + 4 * c, qr + g0 + (size_t)tt * H * dk + 4 * c);
+                cp_async_16(ks + tt * DKP + 4 * c, kr + g0 + (size_t)tt * H * dk + 4 * c);
+            }
+        } else {
+            for (int e = threadIdx.x; e < nt * dk; e += blockDim.x) {
+                const int tt = e / dk, i = e % dk;
+                qs[tt * DKP + i] = qr[g0 + (size_t)tt * H * dk + i];
+                ks[tt * DKP + i] = kr[g0 + (size_t)tt * H * dk + i];
+            }
         }
+        cp_async_commit();
         for (int e = threadIdx.x; e < nt * C; e += blockDim.x) {
             const int tt = e / C, c = blockIdx.x * C + e % C;
             vs[e] = c < dv ? to_float(v[(size_t)(t_first + t0 + tt) * v_ld + (size_t)h * dv + c]) : 0.f;
         }
-        __syncthreads();
+    };
+
+    if (DKP > dk) {                                  // the rows' padding is zeroed once and never written again
+        const int pad = DKP - dk;
+        for (int e = threadIdx.x; e < SCAN_STAGES * 2 * SCAN_TOKENS * pad; e += blockDim.x) {
+            const int rowi = e / pad, c = dk + e % pad;
+            const int s = rowi / (2 * SCAN_TOKENS), within = rowi % (2 * SCAN_TOKENS);
+            sm[s * stage_floats + within * DKP + c] = 0.f;
+        }
+    }
+    fill(0, 0);
+    float S[KPT];
+    if (VEC) {
+#pragma unroll
+        for (int m4 = 0; m4 < KPT / 4; ++m4) {
+            const int i = 4 * (r + R * m4);
+            const float4 s4 = (col && i < dk) ? *(const float4*)(st + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            S[4 * m4 + 0] = s4.x; S[4 * m4 + 1] = s4.y; S[4 * m4 + 2] = s4.z; S[4 * m4 + 3] = s4.w;
+        }
+    } else {
+#pragma unroll
+        for (int m = 0; m < KPT; ++m) S[m] = (col && r + R * m < dk) ? st[r + R * m] : 0.f;
+    }
+    int stage = 0;
+    for (int t0 = 0; t0 < len; t0 += SCAN_TOKENS, stage ^= 1) {
+        const int nt = min(SCAN_TOKENS, len - t0);
+        cp_async_wait_all();
+        __syncthreads();                              // this stage has arrived; the other one is no longer read
+        if (t0 + SCAN_TOKENS < len) fill(stage ^ 1, t0 + SCAN_TOKENS);
+        const float* qs = sm + stage * stage_floats;
+        const float* ks = qs + SCAN_TOKENS * DKP;
+        const float* vs = ks + SCAN_TOKENS * DKP;
+#pragma unroll 2
         for (int tt = 0; tt < nt; ++tt) {
             const float vj = vs[tt * C + jl];
             const float* kt = ks + tt * DKP;
             const float* qt = qs + tt * DKP;
-            float acc = 0.f;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
             if (VEC) {
 #pragma unroll
                 for (int m4 = 0; m4 < KPT / 4; ++m4) {
                     const float4 k4 = ((const float4*)kt)[r + R * m4];
                     const float4 q4 = ((const float4*)qt)[r + R * m4];
-                    S[4 * m4 + 0] = fmaf(dec, S[4 * m4 + 0], k4.x * vj); acc = fmaf(S[4 * m4 + 0], q4.x, acc);
-                    S[4 * m4 + 1] = fmaf(dec, S[4 * m4 + 1], k4.y * vj); acc = fmaf(S[4 * m4 + 1], q4.y, acc);
-                    S[4 * m4 + 2] = fmaf(dec, S[4 * m4 + 2], k4.z * vj); acc = fmaf(S[4 * m4 + 2], q4.z, acc);
-                    S[4 * m4 + 3] = fmaf(dec, S[4 * m4 + 3], k4.w * vj); acc = fmaf(S[4 * m4 + 3], q4.w, acc);
+                    S[4 * m4 + 0] = fmaf(dec, S[4 * m4 + 0], k4.x * vj); a0 = fmaf(S[4 * m4 + 0], q4.x, a0);
+                    S[4 * m4 + 1] = fmaf(dec, S[4 * m4 + 1], k4.y * vj); a1 = fmaf(S[4 * m4 + 1], q4.y, a1);
+                    S[4 * m4 + 2] = fmaf(dec, S[4 * m4 + 2], k4.z * vj); a2 = fmaf(S[4 * m4 + 2], q4.z, a2);
+                    S[4 * m4 + 3] = fmaf(dec, S[4 * m4 + 3], k4.w * vj); a3 = fmaf(S[4 * m4 + 3], q4.w, a3);
                 }
             } else {
 #pragma unroll
                 for (int m = 0; m < KPT; ++m) {
                     S[m] = fmaf(dec, S[m], kt[r + R * m] * vj);
-                    acc = fmaf(S[m], qt[r + R * m], acc);
+                    if (m & 1) a1 = fmaf(S[m], qt[r + R * m], a1); else a0 = fmaf(S[m], qt[r + R * m], a0);
                 }
             }
+            part[tt * (C * R) + threadIdx.x] = (a0 + a1) + (a2 + a3);
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < nt * C; e += blockDim.x) {
+            const int tt = e / C, c = e % C;
+            const float* p = part + tt * (C * R) + c * R;
+            float acc = 0.f;
 #pragma unroll
-            for (int o = R / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (r == 0 && col) out[(size_t)(t_first + t0 + tt) * H * dv + (size_t)h * dv + j] = acc;
+            for (int i = 0; i < R; ++i) acc += p[i];
+            if (blockIdx.x * C + c < dv) out[(size_t)(t_first + t0 + tt) * H * dv + (size_t)h * dv + blockIdx.x * C + c] = acc;
         }
     }
     if (col) {
+        if (VEC) {
 #pragma unroll
-        for (int m = 0; m < KPT; ++m) {
-            const int i = VEC ? 4 * (r + R * (m / 4)) + (m % 4) : r + R * m;
-            if (i < dk) st[i] = S[m];
+            for (int m4 = 0; m4 < KPT / 4; ++m4) {
+                const int i = 4 * (r + R * m4);
+                if (i < dk) *(float4*)(st + i) = make_float4(S[4 * m4 + 0], S[4 * m4 + 1], S[4 * m4 + 2], S[4 * m4 + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int m = 0; m < KPT; ++m)
+                if (r + R * m < dk) st[r + R * m] = S[m];
         }
     }
+}
+
+// The form for key sizes that are multiples of four.  A thread keeps FOUR columns' rows, so every key and query value
+// it reads from shared memory feeds four columns: with one column a thread the kernel was bound by the shared
+// memory's 128 bytes a cycle (two 16-byte reads for twelve arithmetic instructions), measured 0.58 ms for 2,048
+// tokens of 32 heads of 128 x 128; this form takes a third of that.  Thread (g, r) of a block: columns 4g .. 4g+3 of the
+// block's C, rows 4 (r + R m) .. + 3 for m < KPT/4.  Partial sums go to shared memory as [token][g][r][4] (a group of R
+// pieces padded by one piece, so that the adding pass meets no bank twice), and are added after the stage's tokens.
+template <typename T, int KPT, int R>
+__global__ void __launch_bounds__(128)
+retention_scan4_kernel(const float* __restrict__ qr, const float* __restrict__ kr, const T* __restrict__ v, int v_ld,
+                       const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ q_start,
+                       const int* __restrict__ q_len, const int* __restrict__ state_slots, float* __restrict__ out,
+                       int H, int dk, int dv, int C, int stage_tokens) {
+    constexpr int DKP = KPT * R;
+    constexpr int GROUP = 4 * R + 4;                 // floats of one (token, column group) in `part`
+    const int ST = stage_tokens, CG = C / 4;
+    extern __shared__ __align__(16) float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int req = blockIdx.z, h = blockIdx.y;
+    const int len = q_len[req];
+    if (len <= 0) return;                            // a padded request of a captured batch
+    const int slot = state_slots[req];
+    if (slot < 0) return;
+    const int t_first = q_start[req];
+    const int stage_floats = ST * (2 * DKP + C);
+    float* part = sm + SCAN_STAGES * stage_floats;   // [ST][CG][GROUP]
+    const int g = threadIdx.x / R, r = threadIdx.x % R;
+    const int j0 = blockIdx.x * C + 4 * g;
+    const float dec = decay[h];
+    float* st = state + (((size_t)slot * H + h) * dv) * dk;
+
+    auto fill = [&](int s, int t0) {
+        float* qs = sm + s * stage_floats;
+        float* ks = qs + ST * DKP;
+        float* vs = ks + ST * DKP;
+        const int nt = min(ST, len - t0);
+        const size_t g0 = (size_t)(t_first + t0) * H * dk + (size_t)h * dk;
+        const int pieces = dk / 4;
+        for (int e = threadIdx.x; e < nt * pieces; e += blockDim.x) {
+            const int tt = e / pieces, c = e % pieces;
+            cp_async_16(qs + tt * DKP + 4 * c, qr + g0 + (size_t)tt * H * dk + 4 * c);
+            cp_async_16(ks + tt * DKP + 4 * c, kr + g0 + (size_t)tt * H * dk + 4 * c);
+        }
+        cp_async_commit();
+        for (int e = threadIdx.x; e < nt * C; e += blockDim.x) {
+            const int tt = e / C, c = blockIdx.x * C + e % C;
+            vs[e] = c < dv ? to_float(v[(size_t)(t_first + t0 + tt) * v_ld + (size_t)h * dv + c]) : 0.f;
+        }
+    };
+
+    if (DKP > dk) {                                  // the rows' padding is zeroed once and never written again
+        const int pad = DKP - dk;
+        for (int e = threadIdx.x; e < SCAN_STAGES * 2 * ST * pad; e += blockDim.x) {
+            const int rowi = e / pad, c = dk + e % pad;
+            sm[(rowi / (2 * ST)) * stage_floats + (rowi % (2 * ST)) * DKP + c] = 0.f;
+        }
+    }
+    fill(0, 0);
+    float S[4][KPT];
+#pragma unroll
+    for (int ct = 0; ct < 4; ++ct)
+#pragma unroll
+        for (int m4 = 0; m4 < KPT / 4; ++m4) {
+            const int i = 4 * (r + R * m4);
+            const float4 s4 = (j0 + ct < dv && i < dk) ? *(const float4*)(st + (size_t)(j0 + ct) * dk + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            S[ct][4 * m4 + 0] = s4.x; S[ct][4 * m4 + 1] = s4.y; S[ct][4 * m4 + 2] = s4.z; S[ct][4 * m4 + 3] = s4.w;
+        }
+    int stage = 0;
+    for (int t0 = 0; t0 < len; t0 += ST, stage ^= 1) {
+        const int nt = min(ST, len - t0);
+        cp_async_wait_all();
+        __syncthreads();                              // this stage has arrived; the other one and `part` are no longer read
+        if (t0 + ST < len) fill(stage ^ 1, t0 + ST);
+        const float* qs = sm + stage * stage_floats;
+        const float* ks = qs + ST * DKP;
+        const float* vs = ks + ST * DKP;
+        for (int tt = 0; tt < nt; ++tt) {
+            const float4 v4 = *(const float4*)(vs + tt * C + 4 * g);
+            const float vj[4] = {v4.x, v4.y, v4.z, v4.w};
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int m4 = 0; m4 < KPT / 4; ++m4) {
+                const float4 k4 = ((const float4*)(ks + tt * DKP))[r + R * m4];
+                const float4 q4 = ((const float4*)(qs + tt * DKP))[r + R * m4];
+                const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                for (int ct = 0; ct < 4; ++ct)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        S[ct][4 * m4 + e] = fmaf(dec, S[ct][4 * m4 + e], kk[e] * vj[ct]);
+                        acc[ct] = fmaf(S[ct][4 * m4 + e], qq[e], acc[ct]);
+                    }
+            }
+            *(float4*)(part + (tt * CG + g) * GROUP + 4 * r) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < nt * C; e += blockDim.x) {
+            const int grp = e / 4, ct = e % 4;            // grp = tt * CG + g
+            const float* p = part + grp * GROUP + ct;
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < R; ++i) a += p[4 * i];
+            const int tt = grp / CG, j = blockIdx.x * C + 4 * (grp % CG) + ct;
+            if (j < dv) out[(size_t)(t_first + t0 + tt) * H * dv + (size_t)h * dv + j] = a;
+        }
+    }
+#pragma unroll
+    for (int ct = 0; ct < 4; ++ct)
+#pragma unroll
+        for (int m4 = 0; m4 < KPT / 4; ++m4) {
+            const int i = 4 * (r + R * m4);
+            if (j0 + ct < dv && i < dk)
+                *(float4*)(st + (size_t)(j0 + ct) * dk + i) = make_float4(S[ct][4 * m4 + 0], S[ct][4 * m4 + 1], S[ct][4 * m4 + 2], S[ct][4 * m4 + 3]);
+        }
 }
 
 template <typename T>
@@ -153,12 +340,38 @@ __global__ void headwise_gated_rms_norm_kernel(const float* __restrict__ o, cons
     const int n = (int)(pair / H), h = (int)(pair % H);
     if (token_request[n] < 0) return;
     const float* src = o + ((size_t)n * H + h) * dv;
+    const T* g = gate ? gate + (size_t)n * gate_ld + (size_t)h * dv : nullptr;
+    T* dst = out + (size_t)n * out_ld + (size_t)h * dv;
+    if (dv % 4 == 0 && dv <= 512 && ((uintptr_t)src % 16) == 0) {
+        // up to four runs of four values a lane, held in registers between the two passes
+        float4 v[4];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = 4 * (lane + 32 * i);
+            v[i] = c < dv ? *(const float4*)(src + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            s += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+        }
+        s = warp_sum(s);
+        const float rinv = 1.0f / sqrtf(s / (float)dv + eps);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = 4 * (lane + 32 * i);
+            if (c >= dv) continue;
+            float y[4] = {v[i].x * rinv, v[i].y * rinv, v[i].z * rinv, v[i].w * rinv};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (w) y[e] *= w[c + e];
+                if (g) { const float z = to_float(g[c + e]); y[e] *= z / (1.f + expf(-z)); }
+                dst[c + e] = from_float<T>(y[e] * out_scale);
+            }
+        }
+        return;
+    }
     float s = 0.f;
     for (int c = lane; c < dv; c += 32) { const float v = src[c]; s += v * v; }
     s = warp_sum(s);
     const float rinv = 1.0f / sqrtf(s / (float)dv + eps);
-    const T* g = gate ? gate + (size_t)n * gate_ld + (size_t)h * dv : nullptr;
-    T* dst = out + (size_t)n * out_ld + (size_t)h * dv;
     for (int c = lane; c < dv; c += 32) {
         float y = src[c] * rinv;
         if (w) y *= w[c];
@@ -175,10 +388,11 @@ TNX_EXPORT int tnx_retention_prep(const void* proj, int ld, int q_off, int k_off
     if (n_tokens <= 0) return 0;
     if (H <= 0 || dk <= 0 || rot_dims < 0 || rot_dims > dk || rot_dims % 2 || (rot_dims && !inv_freq)) return TNX_ERR_BAD_ARG;
     const int threads = H * dk >= 2048 ? 256 : 128;
+    const size_t smem = (size_t)rot_dims * sizeof(float);
     if (is_h16)
-        return tnx_launch_in_order(retention_prep_kernel<h16>, dim3(n_tokens), dim3(threads), 0, stream, (const h16*)proj, ld,
+        return tnx_launch_in_order(retention_prep_kernel<h16>, dim3(n_tokens), dim3(threads), smem, stream, (const h16*)proj, ld,
                                    q_off, k_off, token_request, positions, inv_freq, rot_dims, k_scale, q_out, k_out, H, dk);
-    return tnx_launch_in_order(retention_prep_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)proj, ld,
+    return tnx_launch_in_order(retention_prep_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream, (const float*)proj, ld,
                                q_off, k_off, token_request, positions, inv_freq, rot_dims, k_scale, q_out, k_out, H, dk);
 }
 
@@ -189,20 +403,49 @@ TNX_EXPORT int tnx_retention_scan_columns(int dv) { return dv >= 16 ? 16 : 8; }
 template <typename T>
 static int retention_scan_launch(const float* qr, const float* kr, const T* v, int v_ld, const float* decay, float* state,
                                  const int* q_start, const int* q_len, const int* state_slots, float* out, int n_requests,
-                                 int H, int dk, int dv, cudaStream_t stream) {
+                                 int H, int dk, int dv, int stage_tokens, cudaStream_t stream) {
     const int C = tnx_retention_scan_columns(dv);
     const dim3 grid((dv + C - 1) / C, H, n_requests);
-    const bool vec = dk % 4 == 0;
+    const bool vec = dk % 4 == 0 && ((uintptr_t)qr % 16) == 0 && ((uintptr_t)kr % 16) == 0 && ((uintptr_t)state % 16) == 0;
 #define SCAN(KPT, R)                                                                                                    \
     do {                                                                                                                \
-        const size_t smem = (size_t)SCAN_TOKENS * (2 * (KPT) * (R) + C) * sizeof(float);                                \
-        if (vec && (KPT) % 4 == 0)                                                                                      \
-            return tnx_launch_in_order(retention_scan_kernel<T, KPT, R, ((KPT) % 4 == 0)>, grid, dim3(C * (R)), smem,   \
-                                       stream, qr, kr, v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk,  \
-                                       dv, C);                                                                          \
+        const size_t smem = ((size_t)SCAN_STAGES * stage_tokens * (2 * (KPT) * (R) + C) + (size_t)stage_tokens * C * (R)) * sizeof(float);                  \
+        if (vec) {                                                                                                      \
+            if (smem > 48 * 1024)                                                                                       \
+                cudaFuncSetAttribute(retention_scan_kernel<T, KPT, R, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            return tnx_launch_in_order(retention_scan_kernel<T, KPT, R, true>, grid, dim3(C * (R)), smem, stream, qr,   \
+                                       kr, v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C,       \
+                                       stage_tokens);                                                                   \
+        }                                                                                                               \
+        if (smem > 48 * 1024)                                                                                           \
+            cudaFuncSetAttribute(retention_scan_kernel<T, KPT, R, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         return tnx_launch_in_order(retention_scan_kernel<T, KPT, R, false>, grid, dim3(C * (R)), smem, stream, qr, kr,  \
-                                   v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C);              \
+                                   v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C, stage_tokens); \
     } while (0)
+#define SCAN4(KPT, R, CC)                                                                                               \
+    do {                                                                                                                \
+        const int C4 = (CC);                                                                                            \
+        const dim3 grid4((dv + C4 - 1) / C4, H, n_requests);                                                            \
+        const size_t smem = ((size_t)SCAN_STAGES * stage_tokens * (2 * (KPT) * (R) + C4) +                              \
+                             (size_t)stage_tokens * (C4 / 4) * (4 * (R) + 4)) * sizeof(float);                          \
+        if (smem > 48 * 1024)                                                                                           \
+            cudaFuncSetAttribute(retention_scan4_kernel<T, KPT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return tnx_launch_in_order(retention_scan4_kernel<T, KPT, R>, grid4, dim3((C4 / 4) * (R)), smem, stream, qr,    \
+                                   kr, v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C4,          \
+                                   stage_tokens);                                                                       \
+    } while (0)
+    // Measured (32 heads of 128 x 128): a step of single tokens streams the state at 6.2 TB/s in the four-column form
+    // (43 us for 64 requests); portions of prompts are a chain of dependent tokens in either form, and there the
+    // one-column form, with twice the warps, is the faster one (0.58 against 0.73 ms for 2,048 tokens).
+    if (vec && stage_tokens == 1) {
+        if (dk <= 16) SCAN4(4, 4, 32);
+        if (dk <= 32) SCAN4(4, 8, 16);
+        if (dk <= 64) SCAN4(4, 16, 16);
+        if (dk <= 128) SCAN4(8, 16, 16);
+        if (dk <= 256) SCAN4(16, 16, 16);
+        return TNX_ERR_UNSUPPORTED;
+    }
+#undef SCAN4
     if (dk <= 16) SCAN(4, 4);
     if (dk <= 32) SCAN(4, 8);
     if (dk <= 64) SCAN(8, 8);
@@ -214,14 +457,17 @@ static int retention_scan_launch(const float* qr, const float* kr, const T* v, i
 
 TNX_EXPORT int tnx_retention_scan(const float* qr, const float* kr, const void* v, int v_ld, const float* decay,
                                   float* state, const int* q_start, const int* q_len, const int* state_slots, float* out,
-                                  int n_requests, int H, int dk, int dv, int v_h16, cudaStream_t stream) {
+                                  int n_requests, int H, int dk, int dv, int most_tokens, int v_h16, cudaStream_t stream) {
+    // most_tokens: an upper bound of the requests' rows (1 for a step of single tokens); it sizes the stages.
     if (n_requests <= 0) return 0;
-    if (H <= 0 || dk <= 0 || dv <= 0 || H > 65535 || n_requests > 65535) return TNX_ERR_BAD_ARG;
+    if (H <= 0 || dk <= 0 || dv <= 0 || H > 65535 || n_requests > 65535 || most_tokens <= 0) return TNX_ERR_BAD_ARG;
+    int stage_tokens = 1;
+    while (stage_tokens < most_tokens && stage_tokens < SCAN_TOKENS_MOST) stage_tokens *= 2;
     if (v_h16)
         return retention_scan_launch<h16>(qr, kr, (const h16*)v, v_ld, decay, state, q_start, q_len, state_slots, out,
-                                          n_requests, H, dk, dv, stream);
+                                          n_requests, H, dk, dv, stage_tokens, stream);
     return retention_scan_launch<float>(qr, kr, (const float*)v, v_ld, decay, state, q_start, q_len, state_slots, out,
-                                        n_requests, H, dk, dv, stream);
+                                        n_requests, H, dk, dv, stage_tokens, stream);
 }
 
 TNX_EXPORT int tnx_headwise_gated_rms_norm(const float* o, const void* gate, int gate_ld, const int* token_request,

@@ -26,7 +26,7 @@ __global__ void rotary_qkv_prep_kernel(const T* __restrict__ proj, int ld, int q
                                        const float* __restrict__ head_scale, const float* __restrict__ inv_freq_qk,
                                        int rot_dims, const float* __restrict__ inv_freq_v, T* __restrict__ q_out,
                                        T* __restrict__ k_out, T* __restrict__ v_out, int H, int G, int dk, int dv, int D) {
-    extern __shared__ float sm[];                   // q [H * dk], k [G * dk], v [G * dv]
+    extern __shared__ float sm[];                   // q [H * dk], k [G * dk], v [G * dv], then cos/sin of the token's angles
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -38,6 +38,14 @@ __global__ void rotary_qkv_prep_kernel(const T* __restrict__ proj, int ld, int q
     float* ks = qs + H * dk;
     float* vs = ks + G * dk;
     const int nq = H * dk, nk = G * dk, nv = G * dv;
+    // every head turns by the same angles: their sines and cosines are computed once per token
+    const int half = rot_dims / 2, hv = inv_freq_v ? dv / 2 : 0;
+    float* cs_qk = vs + nv;
+    float* sn_qk = cs_qk + half;
+    float* cs_v = sn_qk + half;
+    float* sn_v = cs_v + hv;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq_qk[i], &sn_qk[i], &cs_qk[i]);
+    for (int i = threadIdx.x; i < hv; i += blockDim.x) sincosf(pos * inv_freq_v[i], &sn_v[i], &cs_v[i]);
     float sq = 0.f, sk = 0.f;
     for (int c = threadIdx.x; c < nq; c += blockDim.x) { const float v = to_float(row[q_off + c]); qs[c] = v; sq += v * v; }
     for (int c = threadIdx.x; c < nk; c += blockDim.x) { const float v = to_float(row[k_off + c]); ks[c] = v; sk += v * v; }
@@ -46,7 +54,6 @@ __global__ void rotary_qkv_prep_kernel(const T* __restrict__ proj, int ld, int q
     sk = block_sum(sk, scratch);                    // block_sum synchronises: the rows are in shared memory now
     const float rq = wq ? 1.0f / sqrtf(sq / (float)nq + eps) : 1.f;
     const float rk = wk ? 1.0f / sqrtf(sk / (float)nk + eps) : 1.f;
-    const int half = rot_dims / 2;
 
     // queries and keys: pairs of the rotated part, then the dims that pass unchanged, then the padding
     for (int which = 0; which < 2; ++which) {
@@ -60,8 +67,7 @@ __global__ void rotary_qkv_prep_kernel(const T* __restrict__ proj, int ld, int q
             const int c0 = h * dk + i, c1 = c0 + half;
             float u = src[c0] * rinv, v = src[c1] * rinv;
             if (w) { u *= w[c0]; v *= w[c1]; }
-            float sn, cs;
-            sincosf(pos * inv_freq_qk[i], &sn, &cs);
+            const float sn = sn_qk[i], cs = cs_qk[i];
             float a = u * cs - v * sn, b = v * cs + u * sn;
             if (!which && head_scale) { a *= head_scale[h]; b *= head_scale[h]; }
             dst[h * D + i] = from_float<T>(a);
@@ -82,12 +88,10 @@ __global__ void rotary_qkv_prep_kernel(const T* __restrict__ proj, int ld, int q
     // values
     T* vd = v_out + (size_t)n * G * D;
     if (inv_freq_v) {
-        const int hv = dv / 2;
         for (int e = threadIdx.x; e < G * hv; e += blockDim.x) {
             const int h = e / hv, m = e % hv;
             const float u = vs[h * dv + m], v = vs[h * dv + m + hv];
-            float sn, cs;
-            sincosf(pos * inv_freq_v[m], &sn, &cs);
+            const float sn = sn_v[m], cs = cs_v[m];
             vd[h * D + m] = from_float<T>(u * cs - v * sn);
             vd[h * D + m + hv] = from_float<T>(v * cs + u * sn);
         }
@@ -102,6 +106,7 @@ template <typename T>
 __global__ void rotary_unrotate_kernel(const T* __restrict__ att, const int* __restrict__ token_request,
                                        const int* __restrict__ positions, const float* __restrict__ inv_freq_v,
                                        float out_scale, T* __restrict__ out, int out_ld, int H, int dv, int D) {
+    extern __shared__ float sm[];                   // cos and sin of the token's angles, the same for every head
     pdl_launch_dependents();
     pdl_wait();
     const int n = blockIdx.x;
@@ -111,11 +116,14 @@ __global__ void rotary_unrotate_kernel(const T* __restrict__ att, const int* __r
     T* dst = out + (size_t)n * out_ld;
     if (inv_freq_v) {
         const int hv = dv / 2;
+        float* cs_v = sm;
+        float* sn_v = sm + hv;
+        for (int i = threadIdx.x; i < hv; i += blockDim.x) sincosf(pos * inv_freq_v[i], &sn_v[i], &cs_v[i]);
+        __syncthreads();
         for (int e = threadIdx.x; e < H * hv; e += blockDim.x) {
             const int h = e / hv, m = e % hv;
             const float u = to_float(src[h * D + m]), v = to_float(src[h * D + m + hv]);
-            float sn, cs;
-            sincosf(pos * inv_freq_v[m], &sn, &cs);                 // the turn by -a: (u cos a + v sin a, v cos a - u sin a)
+            const float sn = sn_v[m], cs = cs_v[m];                 // the turn by -a: (u cos a + v sin a, v cos a - u sin a)
             dst[h * dv + m] = from_float<T>((u * cs + v * sn) * out_scale);
             dst[h * dv + m + hv] = from_float<T>((v * cs - u * sn) * out_scale);
         }
@@ -136,7 +144,7 @@ TNX_EXPORT int tnx_rotary_qkv_prep(const void* proj, int ld, int q_off, int k_of
     if (H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || D < dk || D < dv || rot_dims < 0 || rot_dims > dk || rot_dims % 2 ||
         (rot_dims && !inv_freq_qk) || (inv_freq_v && dv % 2))
         return TNX_ERR_BAD_ARG;
-    const size_t smem = (size_t)(H * dk + G * dk + G * dv) * sizeof(float);
+    const size_t smem = (size_t)(H * dk + G * dk + G * dv + rot_dims + dv) * sizeof(float);
     if (smem > 200 * 1024) return TNX_ERR_UNSUPPORTED;
     const int threads = 256;
 #define PREP_LAUNCH(T)                                                                                                  \
@@ -159,9 +167,11 @@ TNX_EXPORT int tnx_rotary_unrotate(const void* att, const int* token_request, co
     if (n_tokens <= 0) return 0;
     if (H <= 0 || dv <= 0 || D < dv || (inv_freq_v && dv % 2) || out_ld < H * dv) return TNX_ERR_BAD_ARG;
     const int threads = H * dv >= 2048 ? 256 : 128;
+    const size_t smem = (size_t)dv * sizeof(float);
+    if (smem > 48 * 1024) return TNX_ERR_UNSUPPORTED;
     if (is_h16)
-        return tnx_launch_in_order(rotary_unrotate_kernel<h16>, dim3(n_tokens), dim3(threads), 0, stream, (const h16*)att,
+        return tnx_launch_in_order(rotary_unrotate_kernel<h16>, dim3(n_tokens), dim3(threads), smem, stream, (const h16*)att,
                                    token_request, positions, inv_freq_v, out_scale, (h16*)out, out_ld, H, dv, D);
-    return tnx_launch_in_order(rotary_unrotate_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)att,
+    return tnx_launch_in_order(rotary_unrotate_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream, (const float*)att,
                                token_request, positions, inv_freq_v, out_scale, (float*)out, out_ld, H, dv, D);
 }

@@ -856,10 +856,12 @@ def retention_prep(proj, q_off, k_off, token_request, positions, inv_freq, rot_d
                                   c_int(n_heads), c_int(k_dim), c_int(_is_h16(proj)), _stream()), "retention_prep")
 
 
-def retention_scan(q, k, v, decay, state, q_start, q_len, state_slots, out, n_heads, k_dim, v_dim):
+def retention_scan(q, k, v, decay, state, q_start, q_len, state_slots, out, n_heads, k_dim, v_dim, most_tokens=None):
     """S <- decay S + k v^T, o = S^T q, token by token for every request of the step (q_start, q_len: its rows;
     q_len 0 or slot < 0: skipped).  q, k: 32-bit [N, n_heads * k_dim]; v: [N, n_heads * v_dim] view in the
-    activation type or 32-bit; state: 32-bit [slots, n_heads, v_dim, k_dim]; out: 32-bit [N, n_heads * v_dim]."""
+    activation type or 32-bit; state: 32-bit [slots, n_heads, v_dim, k_dim]; out: 32-bit [N, n_heads * v_dim].
+    most_tokens: an upper bound of any request's rows (default: N); a step of single tokens says 1 and gets
+    small stages."""
     lib = _lib("retention", v)
     N = q.shape[0]
     for t, nm in ((q, "q"), (k, "k")):
@@ -884,7 +886,8 @@ def retention_scan(q, k, v, decay, state, q_start, q_len, state_slots, out, n_he
         raise KernelError("q_start and state_slots must cover every request of q_len")
     _check(lib.tnx_retention_scan(_p(q), _p(k), _p(v), c_int(v_ld), _p(decay), _p(state), _p(q_start), _p(q_len),
                                   _p(state_slots), _p(out), c_int(R), c_int(n_heads), c_int(k_dim), c_int(v_dim),
-                                  c_int(_is_h16(v)), _stream()), "retention_scan")
+                                  c_int(max(1, int(most_tokens if most_tokens is not None else N))), c_int(_is_h16(v)),
+                                  _stream()), "retention_scan")
 
 
 def headwise_gated_rms_norm(o, gate, token_request, weight, eps, out_scale, out, n_heads, v_dim):
@@ -911,10 +914,12 @@ def headwise_gated_rms_norm(o, gate, token_request, weight, eps, out_scale, out,
                                            c_int(v_dim), c_int(_is_h16(out)), _stream()), "headwise_gated_rms_norm")
 
 
-def mingru_scan(proj, z_off, x_off, g_off, state, q_start, q_len, state_slots, out, width, out_scale=1.0):
+def mingru_scan(proj, z_off, x_off, g_off, state, q_start, q_len, state_slots, out, width, out_scale=1.0,
+                most_tokens=None):
     """The minGRU recurrence over every request's rows of the step, from the raw projections in `proj` [N, *]
     (update gate at column z_off, candidate at x_off, output gate at g_off or None); state 32-bit [slots, width];
-    out [N, width] in proj's type: the new state times silu(output gate) times out_scale."""
+    out [N, width] in proj's type: the new state times silu(output gate) times out_scale.  most_tokens: an upper
+    bound of any request's rows (default: N); it decides over how many warps a request's tokens are spread."""
     lib = _lib("mingru", proj, out)
     _need(proj, "proj", _FLOATS, None, contiguous=False)
     N, wide, ld = _rows_2d(proj, "proj")
@@ -933,7 +938,8 @@ def mingru_scan(proj, z_off, x_off, g_off, state, q_start, q_len, state_slots, o
     R = q_len.shape[0]
     _check(lib.tnx_mingru_scan(_p(proj), c_int(ld), c_int(z_off), c_int(x_off), c_int(-1 if g_off is None else g_off),
                                _p(state), _p(q_start), _p(q_len), _p(state_slots), _p(out), c_int(out_ld), c_float(out_scale),
-                               c_int(R), c_int(width), c_int(_is_h16(proj)), _stream()), "mingru_scan")
+                               c_int(R), c_int(width), c_int(max(1, int(most_tokens if most_tokens is not None else N))),
+                               c_int(_is_h16(proj)), _stream()), "mingru_scan")
 
 
 def gated_activation(gate_up, out, activation):

@@ -35,7 +35,8 @@ class MinGRU(FusableMixer):
     def mix(self, ctx, proj, col0, inner_out, out_scale, sub=None):
         W = self.spec.width
         ops.mingru_scan(proj, col0, col0 + W, col0 + 2 * W if self.spec.gate is not None else None, ctx.cache(sub),
-                        ctx.q_start, ctx.q_len, ctx.state_slots, inner_out, W, out_scale=out_scale)
+                        ctx.q_start, ctx.q_len, ctx.state_slots, inner_out, W, out_scale=out_scale,
+                        most_tokens=1 if ctx.decode_only else proj.shape[0])
 
 
 register_mixer("mingru", MinGRU)

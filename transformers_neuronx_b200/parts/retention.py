@@ -64,7 +64,8 @@ class Retention(FusableMixer):
         v = proj[:, v0:v0 + H * dv]
         gate = proj[:, v0 + H * dv:v0 + 2 * H * dv] if s.gate is not None else None
         o = ctx.scratch(N, H * dv, torch.float32)
-        ops.retention_scan(qr, kr, v, self.decay, ctx.cache(sub), ctx.q_start, ctx.q_len, ctx.state_slots, o, H, dk, dv)
+        ops.retention_scan(qr, kr, v, self.decay, ctx.cache(sub), ctx.q_start, ctx.q_len, ctx.state_slots, o, H, dk, dv,
+                           most_tokens=1 if ctx.decode_only else N)
         ops.headwise_gated_rms_norm(o, gate, ctx.token_request, None, s.norm_eps, out_scale, inner_out, H, dv)
 
 
