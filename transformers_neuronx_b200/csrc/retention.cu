@@ -72,13 +72,15 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // KPT: rows of a column one thread keeps; R: lanes a column's rows are spread over (KPT * R >= k_dim).
 // VEC: k_dim is a multiple of four: a thread's rows come in runs of four (rows 4 (r + R m) .. + 3), read as one
 // 16-byte piece, and the stages are filled with 16-byte asynchronous copies; otherwise with plain loads.
+// VASYNC: the values' rows of the block's columns are whole 16-byte pieces too and are staged the same way, in the
+// type they are stored in (converted where they are used); otherwise plain loads convert them on the way in.
 // The R partial sums of an output are not added with shuffles token by token (a chain of round trips that the few
 // warps of a block cannot hide): every thread leaves its partial sum in shared memory, and after a stage's tokens
 // the block adds them up and stores the outputs.
 // A stage holds q [ST][DKP], k [ST][DKP] (columns from k_dim on stay zero) and v [ST][C], ST = stage_tokens: 32 for
 // portions of prompts, as few as one for a step of single tokens (less shared memory, more blocks an SM).
-template <typename T, int KPT, int R, bool VEC>
-__global__ void __launch_bounds__(256)
+template <typename T, int KPT, int R, bool VEC, bool VASYNC>
+__global__ void __launch_bounds__(128)
 retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr, const T* __restrict__ v, int v_ld,
                       const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ q_start,
                       const int* __restrict__ q_len, const int* __restrict__ state_slots, float* __restrict__ out,
@@ -103,7 +105,7 @@ retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr
     float* st = state + (((size_t)slot * H + h) * dv + (col ? j : 0)) * dk;
 
     // Fills stage `s` with the tokens from t0 on: queries and keys by asynchronous copies (VEC) or plain loads,
-    // values by plain loads (they change type on the way).
+    // values by asynchronous copies in their stored type (VASYNC) or by plain loads that convert them.
     auto fill = [&](int s, int t0) {
         float* qs = sm + s * stage_floats;
         float* ks = qs + SCAN_TOKENS * DKP;
@@ -124,10 +126,22 @@ retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr
                 ks[tt * DKP + i] = kr[g0 + (size_t)tt * H * dk + i];
             }
         }
+        if (VASYNC) {
+            constexpr int PER = 16 / sizeof(T);       // values in a 16-byte piece
+            const int vp = C / PER;
+            T* vraw = (T*)vs;
+            for (int e = threadIdx.x; e < nt * vp; e += blockDim.x) {
+                const int tt = e / vp, c = e % vp;
+                cp_async_16(vraw + tt * C + PER * c,
+                            v + (size_t)(t_first + t0 + tt) * v_ld + (size_t)h * dv + blockIdx.x * C + PER * c);
+            }
+        }
         cp_async_commit();
-        for (int e = threadIdx.x; e < nt * C; e += blockDim.x) {
-            const int tt = e / C, c = blockIdx.x * C + e % C;
-            vs[e] = c < dv ? to_float(v[(size_t)(t_first + t0 + tt) * v_ld + (size_t)h * dv + c]) : 0.f;
+        if (!VASYNC) {
+            for (int e = threadIdx.x; e < nt * C; e += blockDim.x) {
+                const int tt = e / C, c = blockIdx.x * C + e % C;
+                vs[e] = c < dv ? to_float(v[(size_t)(t_first + t0 + tt) * v_ld + (size_t)h * dv + c]) : 0.f;
+            }
         }
     };
 
@@ -161,9 +175,9 @@ retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr
         const float* qs = sm + stage * stage_floats;
         const float* ks = qs + SCAN_TOKENS * DKP;
         const float* vs = ks + SCAN_TOKENS * DKP;
-#pragma unroll 2
+#pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
-            const float vj = vs[tt * C + jl];
+            const float vj = VASYNC ? to_float(((const T*)vs)[tt * C + jl]) : vs[tt * C + jl];
             const float* kt = ks + tt * DKP;
             const float* qt = qs + tt * DKP;
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
@@ -211,10 +225,9 @@ retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr
     }
 }
 
-// The form for key sizes that are multiples of four.  A thread keeps FOUR columns' rows, so every key and query value
-// it reads from shared memory feeds four columns: with one column a thread the kernel was bound by the shared
-// memory's 128 bytes a cycle (two 16-byte reads for twelve arithmetic instructions), measured 0.58 ms for 2,048
-// tokens of 32 heads of 128 x 128; this form takes a third of that.  Thread (g, r) of a block: columns 4g .. 4g+3 of the
+// The form for a step of single tokens (key sizes that are multiples of four).  A thread keeps FOUR columns' rows, so
+// a block streams 4 x as much of the state with the same staging, and every key and query value it reads from shared
+// memory feeds four columns.  Thread (g, r) of a block: columns 4g .. 4g+3 of the
 // block's C, rows 4 (r + R m) .. + 3 for m < KPT/4.  Partial sums go to shared memory as [token][g][r][4] (a group of R
 // pieces padded by one piece, so that the adding pass meets no bank twice), and are added after the stage's tokens.
 template <typename T, int KPT, int R>
@@ -407,19 +420,28 @@ static int retention_scan_launch(const float* qr, const float* kr, const T* v, i
     const int C = tnx_retention_scan_columns(dv);
     const dim3 grid((dv + C - 1) / C, H, n_requests);
     const bool vec = dk % 4 == 0 && ((uintptr_t)qr % 16) == 0 && ((uintptr_t)kr % 16) == 0 && ((uintptr_t)state % 16) == 0;
+    const bool vasync = dv % C == 0 && (C * sizeof(T)) % 16 == 0 && ((uintptr_t)v % 16) == 0 && ((size_t)v_ld * sizeof(T)) % 16 == 0 &&
+                        ((size_t)dv * sizeof(T)) % 16 == 0;
 #define SCAN(KPT, R)                                                                                                    \
     do {                                                                                                                \
         const size_t smem = ((size_t)SCAN_STAGES * stage_tokens * (2 * (KPT) * (R) + C) + (size_t)stage_tokens * C * (R)) * sizeof(float);                  \
+        if (vec && vasync) {                                                                                            \
+            if (smem > 48 * 1024)                                                                                       \
+                cudaFuncSetAttribute(retention_scan_kernel<T, KPT, R, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            return tnx_launch_in_order(retention_scan_kernel<T, KPT, R, true, true>, grid, dim3(C * (R)), smem, stream, \
+                                       qr, kr, v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C,   \
+                                       stage_tokens);                                                                   \
+        }                                                                                                               \
         if (vec) {                                                                                                      \
             if (smem > 48 * 1024)                                                                                       \
-                cudaFuncSetAttribute(retention_scan_kernel<T, KPT, R, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            return tnx_launch_in_order(retention_scan_kernel<T, KPT, R, true>, grid, dim3(C * (R)), smem, stream, qr,   \
-                                       kr, v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C,       \
+                cudaFuncSetAttribute(retention_scan_kernel<T, KPT, R, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            return tnx_launch_in_order(retention_scan_kernel<T, KPT, R, true, false>, grid, dim3(C * (R)), smem, stream, \
+                                       qr, kr, v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C,   \
                                        stage_tokens);                                                                   \
         }                                                                                                               \
         if (smem > 48 * 1024)                                                                                           \
-            cudaFuncSetAttribute(retention_scan_kernel<T, KPT, R, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        return tnx_launch_in_order(retention_scan_kernel<T, KPT, R, false>, grid, dim3(C * (R)), smem, stream, qr, kr,  \
+            cudaFuncSetAttribute(retention_scan_kernel<T, KPT, R, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return tnx_launch_in_order(retention_scan_kernel<T, KPT, R, false, false>, grid, dim3(C * (R)), smem, stream, qr, kr, \
                                    v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C, stage_tokens); \
     } while (0)
 #define SCAN4(KPT, R, CC)                                                                                               \

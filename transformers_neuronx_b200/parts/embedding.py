@@ -86,9 +86,9 @@ class Head(Part):
 
     @property
     def libraries(self):
-        libs = ["layernorm", "gemm_simt", "gemm_tc", "gemv"]
-        if self.final_norm is not None:
-            libs += list(self.final_norm.libraries)
+        libs = ["gemm_simt", "gemm_tc", "gemv"]
+        # without a final norm the rows are picked by a kernel of the LayerNorm library
+        libs += list(self.final_norm.libraries) if self.final_norm is not None else ["layernorm"]
         return tuple(dict.fromkeys(libs))
 
     def tensor_specs(self):

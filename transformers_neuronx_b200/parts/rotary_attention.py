@@ -31,8 +31,11 @@ from .spec import RotaryAttentionSpec
 
 
 class RotaryAttention(FusableMixer):
-    extra_libraries = ("rotary_qkv", "kv_cache", "attention_simt", "attention_prefill", "attention_prefill_tc",
-                       "attention_decode")
+    @property
+    def extra_libraries(self):
+        # the prefill kernel of this head size only: tcgen05 for 64 .. 128, mma.sync for the others
+        prefill = "attention_prefill_tc" if self.pad_dim in (64, 80, 96, 112, 128) else "attention_prefill"
+        return ("rotary_qkv", "kv_cache", "attention_simt", prefill, "attention_decode")
 
     def __init__(self, spec: RotaryAttentionSpec):
         s = self.spec = spec
