@@ -220,6 +220,14 @@ def test_mixed_batches_with_pages_and_slots_used_again(name, dtype):
     compare(m, reqs, steps, res, dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_no_fast_path_takes(dtype):
+    m = _model("R")
+    reqs = _requests(m, [3, 70, 41], seed=600)
+    for steps in (whole_steps(reqs), mixed_steps(reqs, [7, 2, 19, 33], decode_tail=12)):
+        compare(m, reqs, steps, run_trace_inprocess(m.folder, dtype, steps, 64 * 4), dtype)
+
+
 def test_logits_do_not_depend_on_the_cut_or_the_batch_beyond_rounding():
     m = _model("P")
     reqs = _requests(m, [130, 45], seed=500)

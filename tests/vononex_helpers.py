@@ -48,7 +48,14 @@ CONFIG_Q = {"architecture": "Vononex", "vocab": 1003, "width": 256, "postln_alph
                 mingru(384, 192),
                 parallel(left(4, 4, 64, 64, 0.125, 32, 1e5), right(4, 32, 32, [0.9, 0.99, 0.995, 0.9995], 32, 1e4), 0.8, 1.0, None),
                 parallel(left(3, 1, 32, 96, 0.2, 32, 3e4), right(1, 256, 16, [0.98], 256, 1e4), 1.0, 1.5, 128)]}
-CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q}
+# A width and a vocabulary that are no multiples of 8 (the 16-bit engine falls back to the CUDA-core product and to
+# scalar loads everywhere), as many key/value heads as heads, head sizes of 20, a feed-forward narrower than the model.
+CONFIG_R = {"architecture": "Vononex", "vocab": 333, "width": 100, "postln_alpha": 0.8, "norm": {"eps": 1e-5},
+            "init_std": 0.2, "layers": [
+                parallel(left(5, 5, 20, 20, 0.22, 20, 2000.0), right(5, 20, 20, [0.8, 0.9, 0.95, 0.99, 0.999], 20, 2000.0), 1.0, 1.0, 36),
+                mingru(100, None),
+                parallel(left(2, 1, 50, 30, 0.14, 10, 50.0), right(1, 100, 100, [0.97], 0, 1.0), 0.5, 2.0, 70)]}
+CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q, "R": CONFIG_R}
 
 # float32: both sides differ by the order of additions only; every row is held to this.
 # bfloat16: activations are rounded to 8 bits of mantissa between kernels, and these small random models pass
