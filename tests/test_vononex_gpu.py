@@ -128,6 +128,53 @@ def test_retention_scan_carries_its_state_across_cuts_and_requests(H, dk, dv):
     assert float((state[1] - 7.0).abs().max()) == 0.0 and float(state[3].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("H, dk, dv, rot", [(3, 20, 24, 12), (2, 128, 64, 128), (1, 256, 16, 0), (2, 8, 40, 8)])
+def test_retention_for_single_tokens_in_one_kernel(H, dk, dv, rot):
+    """Rotation, state update, output, head-wise norm, gate and scale of a step of single tokens, against the
+    equations: three requests (one of them padding) over four steps, from states that are not zero."""
+    from transformers_neuronx_b200.kernels import ops
+    from transformers_neuronx_b200.parts.rotary import inverse_frequencies
+    g = torch.Generator().manual_seed(21)
+    R, steps, pos0 = 2, 4, [37, 1000]
+    wide = 3 + 2 * H * dk + 2 * H * dv
+    proj = torch.randn(steps, R, wide, generator=g)
+    decay = torch.tensor([0.5, 0.99, 0.9999][:H])
+    state0 = torch.randn(4, H, dv, dk, generator=g) * 0.3
+    slots = [2, 0]
+    state = state0.clone().to(DEV)
+    freq = inverse_frequencies(rot, 300.0, DEV) if rot else None
+    want_state = state0.double().clone()
+    for t in range(steps):
+        out = torch.zeros(3, 5 + H * dv, device=DEV)
+        rows = torch.zeros(3, wide)
+        rows[0], rows[2] = proj[t, 0], proj[t, 1]                 # row 1 belongs to nobody
+        ok = ops.retention_decode(rows.to(DEV), 3, 3 + H * dk, 3 + 2 * H * dk, 3 + 2 * H * dk + H * dv,
+                                  _i32([pos0[0] + t, 0, pos0[1] + t]), freq, rot, dk ** -0.5, decay.to(DEV), state,
+                                  _i32([0, 1, 2]), _i32([1, 0, 1]), _i32([slots[0], 3, slots[1]]), 1e-5, 0.8, out[:, 5:], H, dk, dv)
+        assert ok
+        for r in range(R):
+            x = proj[t, r].double()
+            p = torch.tensor([pos0[r] + t])
+            q = VP.turn(x[3:3 + H * dk].view(1, H, dk), p, rot, 300.0)[0]
+            k = VP.turn(x[3 + H * dk:3 + 2 * H * dk].view(1, H, dk), p, rot, 300.0)[0] * dk ** -0.5
+            v = x[3 + 2 * H * dk:3 + 2 * H * dk + H * dv].view(H, dv)
+            gate = x[3 + 2 * H * dk + H * dv:].view(H, dv)
+            o = torch.zeros(H, dv, dtype=torch.float64)
+            for h in range(H):
+                S = float(decay[h]) * want_state[slots[r], h].T + torch.outer(k[h], v[h])      # stored [dv, dk]
+                want_state[slots[r], h] = S.T
+                o[h] = S.T @ q[h]
+            want = 0.8 * VP.rms(o, 1e-5) * VP.silu(gate)
+            _close(out[2 * r, 5:].view(H, dv), want, 3e-5 if pos0[r] < 100 else 3e-4)
+        assert float(out[1].abs().max()) == 0.0 and float(out[:, :5].abs().max()) == 0.0
+    _close(state, want_state, 3e-4)
+    assert torch.equal(state[3].cpu(), state0[3]) and torch.equal(state[1].cpu(), state0[1])
+    # sizes it does not take are refused without a launch, for the caller to run the three kernels
+    assert ops.retention_decode(torch.zeros(1, 2 * 6 + 2 * 6, device=DEV), 0, 6, 12, 18, _i32([0]), None, 0, 1.0,
+                                torch.ones(1, device=DEV), torch.zeros(1, 1, 6, 6, device=DEV), _i32([0]), _i32([1]), _i32([0]),
+                                1e-5, 1.0, torch.zeros(1, 6, device=DEV), 1, 6, 6) is False
+
+
 def test_headwise_norm_with_its_gate():
     from transformers_neuronx_b200.kernels import ops
     g = torch.Generator().manual_seed(5)

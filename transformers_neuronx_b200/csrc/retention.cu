@@ -340,6 +340,126 @@ retention_scan4_kernel(const float* __restrict__ qr, const float* __restrict__ k
         }
 }
 
+// A step of single tokens in ONE kernel (key and value sizes that are multiples of four): what retention_prep, the scan
+// and the head-wise norm do, for one (request, head) a block, without the 32-bit q, k and o passing through memory.
+// The block rotates its head's query and key of the request's token into shared memory (k scaled), streams the head's
+// state through registers once (thread (g, r): columns 4g .. 4g+3, rows 4 (r + R m) .. + 3), adds the partial sums of
+// o through shared memory, and then divides o by its root mean square, applies the gate and the scale and stores
+// the activations.  Requests with no row are skipped; the caller uses it only where every request has one row.
+template <typename T, int KPT, int R>
+__global__ void __launch_bounds__(512)
+retention_decode_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, int g_off,
+                        const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dims,
+                        float k_scale, const float* __restrict__ decay, float* __restrict__ state,
+                        const int* __restrict__ q_start, const int* __restrict__ q_len,
+                        const int* __restrict__ state_slots, float eps, float out_scale, T* __restrict__ out, int out_ld,
+                        int H, int dk, int dv) {
+    constexpr int DKP = KPT * R;
+    constexpr int GROUP = 4 * R + 4;
+    extern __shared__ __align__(16) float sm[];      // q [DKP], k [DKP], v [dv4], gate [dv4], part [CG][GROUP], o [dv4]
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int req = blockIdx.y, h = blockIdx.x;
+    if (q_len[req] <= 0) return;                     // a padded request of a captured batch
+    const int slot = state_slots[req];
+    if (slot < 0) return;
+    const int n = q_start[req];
+    const int CG = (dv + 3) / 4, dv4 = 4 * CG;
+    float* qs = sm;
+    float* ks = qs + DKP;
+    float* vs = ks + DKP;
+    float* gs = vs + dv4;
+    float* part = gs + dv4;
+    float* os = part + CG * GROUP;
+    const T* row = proj + (size_t)n * ld;
+    const float pos = (float)positions[n];
+    const int half = rot_dims / 2;
+    for (int i = threadIdx.x; i < DKP; i += blockDim.x) {
+        float qv = 0.f, kv = 0.f;
+        if (i < dk) {
+            const int c = h * dk + i;
+            qv = to_float(row[q_off + c]);
+            kv = to_float(row[k_off + c]);
+            if (i < rot_dims) {
+                const int fi = i < half ? i : i - half;
+                float sn, cs;
+                sincosf(pos * inv_freq[fi], &sn, &cs);
+                const int partner = i < half ? c + half : c - half;
+                const float q2 = to_float(row[q_off + partner]), k2 = to_float(row[k_off + partner]);
+                // the pair (u, v) becomes (u cos - v sin, v cos + u sin)
+                qv = i < half ? qv * cs - q2 * sn : qv * cs + q2 * sn;
+                kv = i < half ? kv * cs - k2 * sn : kv * cs + k2 * sn;
+            }
+            kv *= k_scale;
+        }
+        qs[i] = qv;
+        ks[i] = kv;
+    }
+    for (int j = threadIdx.x; j < dv4; j += blockDim.x) {
+        vs[j] = j < dv ? to_float(row[v_off + h * dv + j]) : 0.f;
+        gs[j] = (j < dv && g_off >= 0) ? to_float(row[g_off + h * dv + j]) : 0.f;
+    }
+    __syncthreads();
+    const int g = threadIdx.x / R, r = threadIdx.x % R;
+    const float dec = decay[h];
+    float* st = state + (((size_t)slot * H + h) * dv) * dk;
+    if (g < CG) {
+        const float4 v4 = *(const float4*)(vs + 4 * g);
+        const float vj[4] = {v4.x, v4.y, v4.z, v4.w};
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        float4 S[4][KPT / 4];
+        // every piece of the state this thread owns is asked for before the first one is used
+#pragma unroll
+        for (int ct = 0; ct < 4; ++ct)
+#pragma unroll
+            for (int m4 = 0; m4 < KPT / 4; ++m4) {
+                const int i = 4 * (r + R * m4);
+                S[ct][m4] = (4 * g + ct < dv && i < dk) ? *(const float4*)(st + (size_t)(4 * g + ct) * dk + i)
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+        for (int m4 = 0; m4 < KPT / 4; ++m4) {
+            const int i = 4 * (r + R * m4);            // rows beyond k_dim read the zero padding of q and k
+            const float4 k4 = *(const float4*)(ks + i), q4 = *(const float4*)(qs + i);
+#pragma unroll
+            for (int ct = 0; ct < 4; ++ct) {
+                float4& s4 = S[ct][m4];
+                s4.x = fmaf(dec, s4.x, k4.x * vj[ct]); acc[ct] = fmaf(s4.x, q4.x, acc[ct]);
+                s4.y = fmaf(dec, s4.y, k4.y * vj[ct]); acc[ct] = fmaf(s4.y, q4.y, acc[ct]);
+                s4.z = fmaf(dec, s4.z, k4.z * vj[ct]); acc[ct] = fmaf(s4.z, q4.z, acc[ct]);
+                s4.w = fmaf(dec, s4.w, k4.w * vj[ct]); acc[ct] = fmaf(s4.w, q4.w, acc[ct]);
+            }
+        }
+#pragma unroll
+        for (int ct = 0; ct < 4; ++ct)
+#pragma unroll
+            for (int m4 = 0; m4 < KPT / 4; ++m4) {
+                const int i = 4 * (r + R * m4);
+                if (4 * g + ct < dv && i < dk) *(float4*)(st + (size_t)(4 * g + ct) * dk + i) = S[ct][m4];
+            }
+        *(float4*)(part + g * GROUP + 4 * r) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    }
+    __syncthreads();
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+        const float* p = part + (j / 4) * GROUP + (j % 4);
+        float a = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) a += p[4 * i];
+        os[j] = a;
+        ss += a * a;
+    }
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)dv + eps);
+    T* dst = out + (size_t)n * out_ld + (size_t)h * dv;
+    for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+        float y = os[j] * rinv;
+        if (g_off >= 0) { const float z = gs[j]; y *= z / (1.f + expf(-z)); }
+        dst[j] = from_float<T>(y * out_scale);
+    }
+}
+
 template <typename T>
 __global__ void headwise_gated_rms_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_ld,
                                                const int* __restrict__ token_request, const float* __restrict__ w,
@@ -507,4 +627,50 @@ TNX_EXPORT int tnx_headwise_gated_rms_norm(const float* o, const void* gate, int
     return tnx_launch_in_order(headwise_gated_rms_norm_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, o,
                                (const float*)gate, gate_ld, token_request, w, eps, out_scale, (float*)out, out_ld, n_tokens,
                                H, dv);
+}
+
+// One token per request: rotation, state update, output, head-wise norm, gate and scale in one kernel.  Returns
+// TNX_ERR_UNSUPPORTED for sizes it does not take (the caller then runs the three kernels); g_off < 0: no gate.
+template <typename T>
+static int retention_decode_launch(const T* proj, int ld, int q_off, int k_off, int v_off, int g_off, const int* positions,
+                                   const float* inv_freq, int rot_dims, float k_scale, const float* decay, float* state,
+                                   const int* q_start, const int* q_len, const int* state_slots, float eps, float out_scale,
+                                   T* out, int out_ld, int n_requests, int H, int dk, int dv, cudaStream_t stream) {
+    const int CG = (dv + 3) / 4;
+#define RDEC(KPT, R)                                                                                                    \
+    do {                                                                                                                \
+        const int threads = ((CG * (R) + 31) / 32) * 32;                                                                \
+        if (threads > 512) return TNX_ERR_UNSUPPORTED;                                                                  \
+        const size_t smem = (size_t)(2 * (KPT) * (R) + 3 * 4 * CG + CG * (4 * (R) + 4)) * sizeof(float);                \
+        if (smem > 48 * 1024) return TNX_ERR_UNSUPPORTED;                                                               \
+        return tnx_launch_in_order(retention_decode_kernel<T, KPT, R>, dim3(H, n_requests), dim3(threads), smem, stream, \
+                                   proj, ld, q_off, k_off, v_off, g_off, positions, inv_freq, rot_dims, k_scale, decay, \
+                                   state, q_start, q_len, state_slots, eps, out_scale, out, out_ld, H, dk, dv);         \
+    } while (0)
+    if (dk <= 16) RDEC(4, 4);
+    if (dk <= 32) RDEC(4, 8);
+    if (dk <= 64) RDEC(4, 16);
+    if (dk <= 128) RDEC(8, 16);
+    if (dk <= 256) RDEC(16, 16);
+    return TNX_ERR_UNSUPPORTED;
+#undef RDEC
+}
+
+TNX_EXPORT int tnx_retention_decode(const void* proj, int ld, int q_off, int k_off, int v_off, int g_off,
+                                    const int* positions, const float* inv_freq, int rot_dims, float k_scale,
+                                    const float* decay, float* state, const int* q_start, const int* q_len,
+                                    const int* state_slots, float eps, float out_scale, void* out, int out_ld,
+                                    int n_requests, int H, int dk, int dv, int is_h16, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (H <= 0 || dk <= 0 || dv <= 0 || H > 65535 || n_requests > 65535 || rot_dims < 0 || rot_dims > dk || rot_dims % 2 ||
+        (rot_dims && !inv_freq) || out_ld < H * dv)
+        return TNX_ERR_BAD_ARG;
+    if (dk % 4 || dv % 4 || ((uintptr_t)state % 16)) return TNX_ERR_UNSUPPORTED;
+    if (is_h16)
+        return retention_decode_launch<h16>((const h16*)proj, ld, q_off, k_off, v_off, g_off, positions, inv_freq, rot_dims,
+                                            k_scale, decay, state, q_start, q_len, state_slots, eps, out_scale, (h16*)out,
+                                            out_ld, n_requests, H, dk, dv, stream);
+    return retention_decode_launch<float>((const float*)proj, ld, q_off, k_off, v_off, g_off, positions, inv_freq, rot_dims,
+                                          k_scale, decay, state, q_start, q_len, state_slots, eps, out_scale, (float*)out,
+                                          out_ld, n_requests, H, dk, dv, stream);
 }

@@ -890,6 +890,41 @@ def retention_scan(q, k, v, decay, state, q_start, q_len, state_slots, out, n_he
                                   _stream()), "retention_scan")
 
 
+def retention_decode(proj, q_off, k_off, v_off, g_off, positions, inv_freq, rot_dims, k_scale, decay, state, q_start, q_len,
+                     state_slots, eps, out_scale, out, n_heads, k_dim, v_dim) -> bool:
+    """A step in which every request has ONE row: retention_prep, retention_scan and headwise_gated_rms_norm in one
+    kernel (the 32-bit queries, keys and outputs never pass through memory).  Returns False, having launched nothing,
+    for sizes the kernel does not take (k_dim or v_dim no multiple of four, very wide heads): the caller then runs the
+    three kernels.  g_off None: no gate."""
+    lib = _lib("retention", proj, out)
+    _need(proj, "proj", _FLOATS, None, contiguous=False)
+    N, width, ld = _rows_2d(proj, "proj")
+    offs = [q_off + n_heads * k_dim, k_off + n_heads * k_dim, v_off + n_heads * v_dim] + \
+           ([g_off + n_heads * v_dim] if g_off is not None else [])
+    if max(offs) > width:
+        raise KernelError("the projection is narrower than its q/k/v/gate columns")
+    _need(state, "state", torch.float32, 4)
+    if tuple(state.shape[1:]) != (n_heads, v_dim, k_dim):
+        raise KernelError(f"state must be [slots, {n_heads}, {v_dim}, {k_dim}]")
+    _need(out, "out", proj.dtype, None, contiguous=False)
+    No, wo, out_ld = _rows_2d(out, "out")
+    if (No, wo) != (N, n_heads * v_dim):
+        raise KernelError(f"out must be [{N}, {n_heads * v_dim}]")
+    _f32_vec(decay, "decay", n_heads)
+    _f32_vec(inv_freq, "inv_freq", rot_dims // 2 if rot_dims else None)
+    for t, nm in ((positions, "positions"), (q_start, "q_start"), (q_len, "q_len"), (state_slots, "state_slots")):
+        _need(t, nm, torch.int32, 1)
+    code = lib.tnx_retention_decode(_p(proj), c_int(ld), c_int(q_off), c_int(k_off), c_int(v_off),
+                                    c_int(-1 if g_off is None else g_off), _p(positions), _p(inv_freq), c_int(rot_dims),
+                                    c_float(k_scale), _p(decay), _p(state), _p(q_start), _p(q_len), _p(state_slots),
+                                    c_float(eps), c_float(out_scale), _p(out), c_int(out_ld), c_int(q_len.shape[0]),
+                                    c_int(n_heads), c_int(k_dim), c_int(v_dim), c_int(_is_h16(proj)), _stream())
+    if code == -2:
+        return False
+    _check(code, "retention_decode")
+    return True
+
+
 def headwise_gated_rms_norm(o, gate, token_request, weight, eps, out_scale, out, n_heads, v_dim):
     """out = o / rms(o over each head's v_dim dims) (* weight) * silu(gate) * out_scale; o 32-bit [N, n_heads * v_dim],
     gate (optional) and out views in the activation type."""

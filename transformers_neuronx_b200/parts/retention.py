@@ -56,6 +56,14 @@ class Retention(FusableMixer):
     def mix(self, ctx, proj, col0, inner_out, out_scale, sub=None):
         s, N = self.spec, proj.shape[0]
         H, dk, dv = s.n_heads, s.k_dim, s.v_dim
+        rot = s.rotary.dims if s.rotary is not None else 0
+        v0 = col0 + 2 * H * dk
+        # a step of single tokens: one kernel does the rotation, the state's update, the output and its norm
+        if ctx.decode_only and ops.retention_decode(
+                proj, col0, col0 + H * dk, v0, v0 + H * dv if s.gate is not None else None, ctx.positions, self.inv_freq,
+                rot, s.k_scale, self.decay, ctx.cache(sub), ctx.q_start, ctx.q_len, ctx.state_slots, s.norm_eps, out_scale,
+                inner_out, H, dk, dv):
+            return
         qr = ctx.scratch(N, H * dk, torch.float32)
         kr = ctx.scratch(N, H * dk, torch.float32)
         ops.retention_prep(proj, col0, col0 + H * dk, ctx.token_request, ctx.positions, self.inv_freq,
