@@ -14,6 +14,9 @@ is "1,024-token prompts decoded to 2,048"), the percentiles of the step time ove
 decode steps (the reference reports p0/50/90/95/99/100 of its latencies,
 src/transformers_neuronx/generation_demo.py:157-163), and the two further workloads of the baseline:
 OPT-30B sizes decoding at batch 16, and OPT-13B sizes serving 32 requests with a 512-token budget.
+
+`--workload vononex` (a line of its own, not part of the default one): prefill and decode of the Vononex decoder at
+two widths beside OPT at the same width, with every kernel family's time.
 """
 from __future__ import annotations
 

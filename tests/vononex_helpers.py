@@ -42,12 +42,12 @@ CONFIG_P = {"architecture": "Vononex", "vocab": 211, "width": 72, "postln_alpha"
                 mingru(33, 64)]}
 # Sizes the tensor-core kernels take: head sizes 128 and 64 (and 32 beside 96, stored as 96), several key/value
 # heads, retention with 128 rows a column.
-CONFIG_Q = {"architecture": "Vononex", "vocab": 1003, "width": 256, "postln_alpha": 3.0, "norm": {"eps": 1e-6},
+CONFIG_Q = {"architecture": "Vononex", "vocab": 1003, "width": 320, "postln_alpha": 3.0, "norm": {"eps": 1e-6},
             "init_std": 0.12, "layers": [
-                parallel(left(4, 2, 128, 128, 0.09, 128, 10000.0), right(2, 128, 64, [0.96875, 0.999], 64, 1e6), 1.2, 0.9, 320),
-                mingru(384, 192),
-                parallel(left(4, 4, 64, 64, 0.125, 32, 1e5), right(4, 32, 32, [0.9, 0.99, 0.995, 0.9995], 32, 1e4), 0.8, 1.0, None),
-                parallel(left(3, 1, 32, 96, 0.2, 32, 3e4), right(1, 256, 16, [0.98], 256, 1e4), 1.0, 1.5, 128)]}
+                parallel(left(4, 2, 128, 128, 0.09, 128, 20000.0), right(2, 128, 64, [0.96875, 0.999], 64, 5e5), 1.3, 0.7, 384),
+                mingru(448, 192),
+                parallel(left(4, 4, 64, 64, 0.125, 32, 1e5), right(4, 32, 32, [0.9, 0.99, 0.995, 0.9995], 32, 3e4), 0.8, 1.0, None),
+                parallel(left(3, 1, 32, 96, 0.2, 32, 3e4), right(1, 256, 16, [0.98], 256, 7e3), 1.0, 1.5, 128)]}
 # A width and a vocabulary that are no multiples of 8 (the 16-bit engine falls back to the CUDA-core product and to
 # scalar loads everywhere), as many key/value heads as heads, head sizes of 20, a feed-forward narrower than the model.
 CONFIG_R = {"architecture": "Vononex", "vocab": 333, "width": 100, "postln_alpha": 0.8, "norm": {"eps": 1e-5},
