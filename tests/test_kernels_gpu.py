@@ -471,6 +471,41 @@ def test_attention_decode_appends_the_new_token(n_heads, n_kv, d, n_splits, warp
     assert bool(torch.isnan(case.cache.float()[~written]).all()), "nothing else was written"
 
 
+@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 2, 128), (8, 2, 64), (8, 2, 128), (4, 1, 80), (2, 1, 112), (4, 2, 96), (6, 2, 64)])
+@pytest.mark.parametrize("window", [None, 50])
+@pytest.mark.parametrize("n_splits,warps", [(None, None), (1, 4), (3, 4), (1, 8), (5, 8), (3, 16), (44, 4)])
+def test_attention_decode_with_a_key_value_heads_query_heads_in_one_block(n_heads, n_kv, d, window, n_splits, warps):
+    """Grouped key/value heads: a block takes the 2 or 4 query heads of a key/value head and reads its pages once;
+    sizes the grouped form does not take (3 query heads a key/value head, head size 96) run one block a head.  With and
+    without the cache append, twice (the split counters must be back at zero)."""
+    lens = [(0, 1), (15, 1), (16, 1), (17, 1), (255, 1), (256, 1), (700, 1), (63, 1)]
+    case = PagedCase(lens, n_heads, n_kv, d, torch.bfloat16, seed=d + 5)
+    scale = 0.8 / math.sqrt(d)
+    out = torch.zeros(case.N, n_heads * d, dtype=torch.bfloat16, device=DEV)
+    o = ops()
+    for _ in range(2):
+        out.zero_()
+        o.attention_decode(case.q_flat, case.cache, case.bt, case.tok_req, case.positions, out, n_heads, scale,
+                           window or 0, max_kv_len=701, n_splits=n_splits, warps=warps, grouped=True)
+        assert rel_err(out, case.want(scale, window)) <= 1e-2
+    if window is None:
+        full = case.cache.clone()
+        k_new = torch.zeros(case.N, n_kv * d, dtype=torch.bfloat16, device=DEV)
+        v_new = torch.zeros(case.N, n_kv * d, dtype=torch.bfloat16, device=DEV)
+        pages = case.bt.cpu()
+        for r, (c, _) in enumerate(lens):
+            pg, slot = int(pages[r, c // 16]), c % 16
+            k_new[r] = full[pg, 0, :, slot].reshape(-1)
+            v_new[r] = full[pg, 1, :, slot].reshape(-1)
+            case.cache[pg, :, :, slot] = float("nan")
+        out.zero_()
+        o.attention_decode(case.q_flat, case.cache, case.bt, case.tok_req, case.positions, out, n_heads, scale, 0,
+                           max_kv_len=701, n_splits=n_splits, warps=warps, new_kv=(k_new, v_new), grouped=True)
+        assert rel_err(out, case.want(scale, None)) <= 1e-2
+        written = ~torch.isnan(full.float())
+        assert torch.equal(case.cache[written], full[written])
+
+
 def test_attention_decode_row_list():
     """Only the rows named are computed (a mixed batch: the others belong to the prefill kernel)."""
     lens = [(5, 1), (0, 40), (99, 1), (10, 3), (33, 1)]

@@ -48,19 +48,24 @@ struct DecodeParams {
 // key).  KPL = 32 / LPK keys are read per warp-wide load.  E = 1 serves the head sizes whose number of
 // 8-dim pieces is a power of two (and, with idle lanes, any other); E = 3 gives head sizes like 96
 // (4 x 3 pieces) a layout without idle lanes.
-template <int LPK, int E, int WARPS>
+// REP: query heads a block takes.  With REP > 1 (grouped key/value heads: REP = query heads per key/value head, 2 or
+// 4) a block takes ALL query heads of one key/value head, so that the head's pages are read once and every key and
+// value loaded feeds REP dot products and accumulators; with one block per query head the heads of a group each
+// stream the group's pages (measured at batch 64 with 4 query heads a key/value head: 308 us a layer where the pages'
+// own streaming takes 81).
+template <int LPK, int E, int WARPS, int REP>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const DecodeParams p) {
     constexpr int KPL = 32 / LPK;
     constexpr int GROUPS = PAGE / KPL;         // key groups (of KPL keys) per page
     constexpr int LOADS = GROUPS * E;          // warp-wide loads per page and tensor (LPK = 32: 16, LPK = 2, E = 1: 1)
-    __shared__ float sm_m[WARPS], sm_l[WARPS];
-    __shared__ float sm_acc[WARPS][LPK * E * 8];
+    __shared__ float sm_m[REP][WARPS], sm_l[REP][WARPS];
+    __shared__ float sm_acc[REP][WARPS][LPK * E * 8];
     __shared__ int last_flag;
     pdl_launch_dependents();
     pdl_wait();
 
-    const int h = blockIdx.x, ri = blockIdx.y, split = blockIdx.z;
+    const int h0 = blockIdx.x * REP, ri = blockIdx.y, split = blockIdx.z;       // the block's first query head
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // The loads a block needs before its first page are a chain (row -> request -> block table -> page);
     // what does not depend on the link before it is asked for at once.
@@ -72,31 +77,39 @@ attention_decode_kernel(const DecodeParams p) {
     const int sub = lane % LPK;                                  // which 8 dims (of each of its E pieces)
     const int kgrp = lane / LPK;                                 // which key of a load
     const bool dim_ok = E > 1 || sub * 8 < d;                    // with E > 1 the head size is exactly LPK * E * 8
-    uint4 q_raw[E];
+    uint4 q_raw[REP][E];
 #pragma unroll
-    for (int e = 0; e < E; ++e)
-        q_raw[e] = dim_ok ? *(const uint4*)(p.q + (size_t)row * p.q_stride + (size_t)h * d + (e * LPK + sub) * 8) : make_uint4(0, 0, 0, 0);
+    for (int x = 0; x < REP; ++x)
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+            q_raw[x][e] = dim_ok ? *(const uint4*)(p.q + (size_t)row * p.q_stride + (size_t)(h0 + x) * d + (e * LPK + sub) * 8) : make_uint4(0, 0, 0, 0);
     if (req < 0) return;                                        // a padded row of a captured batch
     const int kv_len = pos + 1;
     const int first_key = (p.window > 0 && kv_len > p.window) ? kv_len - p.window : 0;
-    const int kvh = h / (p.n_heads / p.n_kv_heads);
+    const int kvh = h0 / (p.n_heads / p.n_kv_heads);
     const int* bt = p.block_tables + (size_t)req * p.bt_stride;
 
-    float q[E][8];
+    float q[REP][E][8];
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-        const h16x2* qq = (const h16x2*)&q_raw[e];
+    for (int x = 0; x < REP; ++x)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = h16x2_to_float2(qq[i]);
-            q[e][2 * i] = f.x * p.scale; q[e][2 * i + 1] = f.y * p.scale;
+        for (int e = 0; e < E; ++e) {
+            const h16x2* qq = (const h16x2*)&q_raw[x][e];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = h16x2_to_float2(qq[i]);
+                q[x][e][2 * i] = f.x * p.scale; q[x][e][2 * i + 1] = f.y * p.scale;
+            }
         }
+    float m[REP], l[REP], acc[REP][E][8];
+#pragma unroll
+    for (int x = 0; x < REP; ++x) {
+        m[x] = -INFINITY; l[x] = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[x][e][i] = 0.f;
     }
-    float m = -INFINITY, l = 0.f, acc[E][8];
-#pragma unroll
-    for (int e = 0; e < E; ++e)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[e][i] = 0.f;
 
     const int n_pages = (kv_len + PAGE - 1) / PAGE;
     const int page_lo = max(split * p.pages_per_split, first_key / PAGE);
@@ -141,54 +154,70 @@ attention_decode_kernel(const DecodeParams p) {
     auto consume = [&](int t, uint4 (&kb)[CH], uint4 (&vb)[CH]) {
         const int pg = page_lo + warp + (t / CPP) * WARPS;
         const int g0 = (t % CPP) * CG;
-        float s[CG];
-        float chunk_max = -INFINITY;
+        float s[REP][CG];
+        float chunk_max[REP];
+#pragma unroll
+        for (int x = 0; x < REP; ++x) chunk_max[x] = -INFINITY;
 #pragma unroll
         for (int g = 0; g < CG; ++g) {
-            float dot = 0.f;
-#pragma unroll
-            for (int e = 0; e < E; ++e) {                        // one chain of multiply-adds per piece, not one for all
-                const h16x2* kk = (const h16x2*)&kb[g * E + e];
-                float de = 0.f;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float2 f = h16x2_to_float2(kk[u]);
-                    de = fmaf(q[e][2 * u], f.x, de);
-                    de = fmaf(q[e][2 * u + 1], f.y, de);
-                }
-                dot += de;
-            }
-#pragma unroll
-            for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
             const int j = pg * PAGE + (g0 + g) * KPL + kgrp;
-            s[g] = (j >= first_key && j < cached_len) ? dot : -INFINITY;
-            chunk_max = fmaxf(chunk_max, s[g]);
+            const bool seen = j >= first_key && j < cached_len;          // the same for every head
+#pragma unroll
+            for (int x = 0; x < REP; ++x) {
+                float dot = 0.f;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {                    // one chain of multiply-adds per piece, not one for all
+                    const h16x2* kk = (const h16x2*)&kb[g * E + e];
+                    float de = 0.f;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float2 f = h16x2_to_float2(kk[u]);
+                        de = fmaf(q[x][e][2 * u], f.x, de);
+                        de = fmaf(q[x][e][2 * u + 1], f.y, de);
+                    }
+                    dot += de;
+                }
+#pragma unroll
+                for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                s[x][g] = seen ? dot : -INFINITY;
+                chunk_max[x] = fmaxf(chunk_max[x], s[x][g]);
+            }
         }
 #pragma unroll
-        for (int o = 16; o >= LPK; o >>= 1) chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, o));
-        if (chunk_max == -INFINITY) return;                      // every key of the chunk masked (warp-uniform)
-        const float m_new = fmaxf(m, chunk_max);
-        const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
-        l *= corr;
+        for (int x = 0; x < REP; ++x)
 #pragma unroll
-        for (int e = 0; e < E; ++e)
+            for (int o = 16; o >= LPK; o >>= 1) chunk_max[x] = fmaxf(chunk_max[x], __shfl_xor_sync(0xffffffffu, chunk_max[x], o));
+        if (chunk_max[0] == -INFINITY) return;                   // every key of the chunk masked (warp-uniform, and the same for every head)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[e][i] *= corr;
-        m = m_new;
+        for (int x = 0; x < REP; ++x) {
+            const float m_new = fmaxf(m[x], chunk_max[x]);
+            const float corr = (m[x] == -INFINITY) ? 0.f : __expf(m[x] - m_new);
+            l[x] *= corr;
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[x][e][i] *= corr;
+            m[x] = m_new;
+        }
 #pragma unroll
         for (int g = 0; g < CG; ++g) {
-            const bool live = s[g] != -INFINITY;
-            const float pj = live ? __expf(s[g] - m) : 0.f;
-            l += pj;
+            const bool live = s[0][g] != -INFINITY;
 #pragma unroll
-            for (int e = 0; e < E; ++e) {
+            for (int e = 0; e < E; ++e)
                 if (!live) vb[g * E + e] = make_uint4(0, 0, 0, 0);   // rows never written may hold anything, NaN included
-                const h16x2* vv = (const h16x2*)&vb[g * E + e];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float2 f = h16x2_to_float2(vv[u]);
-                    acc[e][2 * u] = fmaf(pj, f.x, acc[e][2 * u]);
-                    acc[e][2 * u + 1] = fmaf(pj, f.y, acc[e][2 * u + 1]);
+            for (int x = 0; x < REP; ++x) {
+                const float pj = live ? __expf(s[x][g] - m[x]) : 0.f;
+                l[x] += pj;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const h16x2* vv = (const h16x2*)&vb[g * E + e];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float2 f = h16x2_to_float2(vv[u]);
+                        acc[x][e][2 * u] = fmaf(pj, f.x, acc[x][e][2 * u]);
+                        acc[x][e][2 * u + 1] = fmaf(pj, f.y, acc[x][e][2 * u + 1]);
+                    }
                 }
             }
         }
@@ -226,92 +255,102 @@ attention_decode_kernel(const DecodeParams p) {
             kown[e] = dim_ok ? *(const uint4*)(ksrc + (e * LPK + sub) * 8) : make_uint4(0, 0, 0, 0);
             vown[e] = dim_ok ? *(const uint4*)(vsrc + (e * LPK + sub) * 8) : make_uint4(0, 0, 0, 0);
         }
-        float dot = 0.f;
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-            const h16x2* kk = (const h16x2*)&kown[e];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const float2 f = h16x2_to_float2(kk[t]);
-                dot = fmaf(q[e][2 * t], f.x, dot);
-                dot = fmaf(q[e][2 * t + 1], f.y, dot);
-            }
-        }
-#pragma unroll
-        for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        const float s_own = __shfl_sync(0xffffffffu, dot, 0);
-        const float m_new = fmaxf(m, s_own);
-        const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
-        l *= corr;
-#pragma unroll
-        for (int e = 0; e < E; ++e)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[e][i] *= corr;
-        m = m_new;
-        if (kgrp == 0) {
-            const float pj = __expf(s_own - m);
-            l += pj;
+        for (int x = 0; x < REP; ++x) {
+            float dot = 0.f;
 #pragma unroll
             for (int e = 0; e < E; ++e) {
-                const h16x2* vv = (const h16x2*)&vown[e];
+                const h16x2* kk = (const h16x2*)&kown[e];
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
-                    const float2 f = h16x2_to_float2(vv[t]);
-                    acc[e][2 * t] = fmaf(pj, f.x, acc[e][2 * t]);
-                    acc[e][2 * t + 1] = fmaf(pj, f.y, acc[e][2 * t + 1]);
+                    const float2 f = h16x2_to_float2(kk[t]);
+                    dot = fmaf(q[x][e][2 * t], f.x, dot);
+                    dot = fmaf(q[x][e][2 * t + 1], f.y, dot);
+                }
+            }
+#pragma unroll
+            for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            const float s_own = __shfl_sync(0xffffffffu, dot, 0);
+            const float m_new = fmaxf(m[x], s_own);
+            const float corr = (m[x] == -INFINITY) ? 0.f : __expf(m[x] - m_new);
+            l[x] *= corr;
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[x][e][i] *= corr;
+            m[x] = m_new;
+            if (kgrp == 0) {
+                const float pj = __expf(s_own - m[x]);
+                l[x] += pj;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const h16x2* vv = (const h16x2*)&vown[e];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const float2 f = h16x2_to_float2(vv[t]);
+                        acc[x][e][2 * t] = fmaf(pj, f.x, acc[x][e][2 * t]);
+                        acc[x][e][2 * t + 1] = fmaf(pj, f.y, acc[x][e][2 * t + 1]);
+                    }
                 }
             }
         }
     }
     // lanes with the same dims but other keys -> one accumulator per dim slice; l counted once per key
 #pragma unroll
-    for (int o = 16; o >= LPK; o >>= 1) {
-        l += __shfl_xor_sync(0xffffffffu, l, o);
+    for (int x = 0; x < REP; ++x) {
 #pragma unroll
-        for (int e = 0; e < E; ++e)
+        for (int o = 16; o >= LPK; o >>= 1) {
+            l[x] += __shfl_xor_sync(0xffffffffu, l[x], o);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[e][i] += __shfl_xor_sync(0xffffffffu, acc[e][i], o);
+            for (int e = 0; e < E; ++e)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[x][e][i] += __shfl_xor_sync(0xffffffffu, acc[x][e][i], o);
+        }
+        if (lane < LPK) {
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sm_acc[x][warp][(e * LPK + lane) * 8 + i] = acc[x][e][i];
+        }
+        if (lane == 0) { sm_m[x][warp] = m[x]; sm_l[x][warp] = l[x]; }
     }
-    if (lane < LPK) {
-#pragma unroll
-        for (int e = 0; e < E; ++e)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sm_acc[warp][(e * LPK + lane) * 8 + i] = acc[e][i];
-    }
-    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
     __syncthreads();
 
-    // merge the warps
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_m[w]);
-    float L = 0.f, f[WARPS];
+    // merge the warps, head by head
     const int t = threadIdx.x;
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) {
-        f[w] = (sm_m[w] == -INFINITY) ? 0.f : __expf(sm_m[w] - M);
-        L += sm_l[w] * f[w];
-    }
-    for (int t2 = t; t2 < d; t2 += WARPS * 32) {                  // head_dim may exceed the block size
-        float o_val = 0.f;
+    for (int x = 0; x < REP; ++x) {
+        const int h = h0 + x;
+        float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) o_val += sm_acc[w][t2] * f[w];
-        if (p.n_splits == 1) {
-            p.out[(size_t)row * p.out_stride + (size_t)h * d + t2] = float_to_h16(o_val / L);
-        } else {
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_m[x][w]);
+        float L = 0.f, f[WARPS];
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            f[w] = (sm_m[x][w] == -INFINITY) ? 0.f : __expf(sm_m[x][w] - M);
+            L += sm_l[x][w] * f[w];
+        }
+        for (int t2 = t; t2 < d; t2 += WARPS * 32) {                  // head_dim may exceed the block size
+            float o_val = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) o_val += sm_acc[x][w][t2] * f[w];
+            if (p.n_splits == 1) {
+                p.out[(size_t)row * p.out_stride + (size_t)h * d + t2] = float_to_h16(o_val / L);
+            } else {
+                float* dst = p.scratch + (((size_t)ri * p.n_heads + h) * p.n_splits + split) * (d + 2);
+                dst[2 + t2] = o_val;
+            }
+        }
+        if (p.n_splits > 1 && t == 0) {
             float* dst = p.scratch + (((size_t)ri * p.n_heads + h) * p.n_splits + split) * (d + 2);
-            dst[2 + t2] = o_val;
+            dst[0] = M; dst[1] = L;
         }
     }
     if (p.n_splits == 1) return;
-    if (t == 0) {
-        float* dst = p.scratch + (((size_t)ri * p.n_heads + h) * p.n_splits + split) * (d + 2);
-        dst[0] = M; dst[1] = L;
-    }
     __threadfence();
     __syncthreads();
     if (t == 0) {
-        int* c = p.counters + (size_t)ri * p.n_heads + h;
+        int* c = p.counters + (size_t)ri * p.n_heads + h0;          // one counter for the block's heads
         const int prev = atomicAdd(c, 1);
         last_flag = (prev == p.n_splits - 1);
         if (last_flag) *c = 0;
@@ -321,56 +360,86 @@ attention_decode_kernel(const DecodeParams p) {
     __threadfence();
     // Merge in split order.  Loads are issued eight splits at a time before their values are used,
     // so that the merge costs a few round trips to the second-level cache, not one per split.
-    const float* base = p.scratch + ((size_t)ri * p.n_heads + h) * p.n_splits * (d + 2);
-    const size_t stride = (size_t)(d + 2);
-    const int S = p.n_splits;
-    float GM = -INFINITY;
-    for (int s0 = 0; s0 < S; s0 += 8) {
-        float ms[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ms[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride) : -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) GM = fmaxf(GM, ms[i]);
-    }
-    float GL = 0.f;
-    for (int s0 = 0; s0 < S; s0 += 8) {
-        float ms[8], ls[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            ms[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride) : -INFINITY;
-            ls[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride + 1) : 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) GL += (ms[i] == -INFINITY) ? 0.f : ls[i] * __expf(ms[i] - GM);
-    }
-    for (int t2 = t; t2 < d; t2 += WARPS * 32) {
-        float o = 0.f;
+    for (int x = 0; x < REP; ++x) {
+        const int h = h0 + x;
+        const float* base = p.scratch + ((size_t)ri * p.n_heads + h) * p.n_splits * (d + 2);
+        const size_t stride = (size_t)(d + 2);
+        const int S = p.n_splits;
+        float GM = -INFINITY;
         for (int s0 = 0; s0 < S; s0 += 8) {
-            float ms[8], vs[8];
+            float ms[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ms[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride) : -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) GM = fmaxf(GM, ms[i]);
+        }
+        float GL = 0.f;
+        for (int s0 = 0; s0 < S; s0 += 8) {
+            float ms[8], ls[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 ms[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride) : -INFINITY;
-                vs[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride + 2 + t2) : 0.f;
+                ls[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride + 1) : 0.f;
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) if (ms[i] != -INFINITY) o += vs[i] * __expf(ms[i] - GM);
+            for (int i = 0; i < 8; ++i) GL += (ms[i] == -INFINITY) ? 0.f : ls[i] * __expf(ms[i] - GM);
         }
-        p.out[(size_t)row * p.out_stride + (size_t)h * d + t2] = float_to_h16(o / GL);
+        for (int t2 = t; t2 < d; t2 += WARPS * 32) {
+            float o = 0.f;
+            for (int s0 = 0; s0 < S; s0 += 8) {
+                float ms[8], vs[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    ms[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride) : -INFINITY;
+                    vs[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride + 2 + t2) : 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) if (ms[i] != -INFINITY) o += vs[i] * __expf(ms[i] - GM);
+            }
+            p.out[(size_t)row * p.out_stride + (size_t)h * d + t2] = float_to_h16(o / GL);
+        }
     }
 }
 
 // Launches the kernel for LPK lanes a key and E pieces a lane with 4, 8 or 16 warps a block (16 only for
 // E = 1 and at most 16 lanes a key, where the registers allow it; 8 otherwise).
+// rep > 1 (2 or 4, only where gqa_rep() below says so): a block takes the rep query heads of a key/value head, with
+// 4 or 8 warps (their accumulators leave no registers for 16).
 template <int LPK, int E>
-int launch_decode(int warps, dim3 grid, cudaStream_t stream, const DecodeParams& p) {
-    if constexpr (E == 1 && LPK <= 16) {
-        if (warps == 16) return tnx_launch_in_order(attention_decode_kernel<LPK, E, 16>, grid, dim3(16 * 32), 0, stream, p);
+int launch_decode(int warps, int rep, dim3 grid, cudaStream_t stream, const DecodeParams& p) {
+    if constexpr (E == 1 && (LPK == 8 || LPK == 16)) {
+        if (rep == 4) {
+            if (warps >= 8) return tnx_launch_in_order(attention_decode_kernel<LPK, E, 8, 4>, grid, dim3(8 * 32), 0, stream, p);
+            return tnx_launch_in_order(attention_decode_kernel<LPK, E, 4, 4>, grid, dim3(4 * 32), 0, stream, p);
+        }
+        if (rep == 2) {
+            if (warps >= 8) return tnx_launch_in_order(attention_decode_kernel<LPK, E, 8, 2>, grid, dim3(8 * 32), 0, stream, p);
+            return tnx_launch_in_order(attention_decode_kernel<LPK, E, 4, 2>, grid, dim3(4 * 32), 0, stream, p);
+        }
     }
-    if (warps >= 8) return tnx_launch_in_order(attention_decode_kernel<LPK, E, 8>, grid, dim3(8 * 32), 0, stream, p);
-    return tnx_launch_in_order(attention_decode_kernel<LPK, E, 4>, grid, dim3(4 * 32), 0, stream, p);
+    if (rep != 1) return TNX_ERR_UNSUPPORTED;
+    if constexpr (E == 1 && LPK <= 16) {
+        if (warps == 16) return tnx_launch_in_order(attention_decode_kernel<LPK, E, 16, 1>, grid, dim3(16 * 32), 0, stream, p);
+    }
+    if (warps >= 8) return tnx_launch_in_order(attention_decode_kernel<LPK, E, 8, 1>, grid, dim3(8 * 32), 0, stream, p);
+    return tnx_launch_in_order(attention_decode_kernel<LPK, E, 4, 1>, grid, dim3(4 * 32), 0, stream, p);
+}
+
+// How many query heads a block takes for these sizes: the query heads per key/value head where that is 2 or 4 and the
+// head size is one whose 8-dim pieces fill 8 or 16 lanes a key (64, 80 .. 128); 1 otherwise (one block per query head).
+int gqa_rep(int n_heads, int n_kv_heads, int head_dim) {
+    const int group = n_heads / n_kv_heads, chunks = head_dim / 8;
+    const bool lanes_8_or_16 = chunks == 5 || chunks == 7 || chunks == 8 || (chunks > 8 && chunks <= 16 && chunks != 12);
+    return ((group == 2 || group == 4) && lanes_8_or_16) ? group : 1;
 }
 
 }  // namespace
+
+// Query heads a block of the kernel takes for these sizes (the caller plans its blocks with it).
+TNX_EXPORT int tnx_attention_decode_heads_per_block(int n_heads, int n_kv_heads, int head_dim) {
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || head_dim % 8) return 1;
+    return gqa_rep(n_heads, n_kv_heads, head_dim);
+}
 
 // Scratch floats and counters needed for n_rows decode rows with n_splits splits.
 TNX_EXPORT long long tnx_attention_decode_scratch_floats(int n_rows, int n_heads, int head_dim, int n_splits) {
@@ -384,7 +453,10 @@ TNX_EXPORT int tnx_attention_decode_append(const void* q, int q_stride, void* ca
                                            void* out, int out_stride, int n_rows, int n_heads, int n_kv_heads, int head_dim,
                                            int page_size, int window, float scale, int n_splits, int pages_per_split,
                                            float* scratch, int* counters, const void* k_new, const void* v_new,
-                                           int kv_stride, int warps, cudaStream_t stream) {
+                                           int kv_stride, int warps, int heads_per_block, cudaStream_t stream) {
+    // heads_per_block: 1, or what tnx_attention_decode_heads_per_block answers for these sizes (the caller chooses:
+    // taking a key/value head's query heads together pays once there are enough (row, key/value head) pairs to fill
+    // the GPU; with few rows one block per query head spreads the same work over more blocks).
     if (n_rows <= 0) return 0;
     if (page_size != PAGE || head_dim % 16 || head_dim < 16 || head_dim > 256 || n_kv_heads <= 0 ||
         n_heads % n_kv_heads || q_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15))
@@ -400,7 +472,10 @@ TNX_EXPORT int tnx_attention_decode_append(const void* q, int q_stride, void* ca
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.window = window; p.scale = scale;
     p.n_splits = n_splits; p.pages_per_split = pages_per_split; p.scratch = scratch; p.counters = counters;
     p.k_new = (const h16*)k_new; p.v_new = (const h16*)v_new; p.kv_stride = kv_stride; p.cache_w = (h16*)cache;
-    dim3 grid(n_heads, n_rows, n_splits);
+    const int rep = heads_per_block;
+    if (rep != 1 && rep != gqa_rep(n_heads, n_kv_heads, head_dim)) return TNX_ERR_BAD_ARG;
+    if (rep > 1 && warps == 16) warps = 8;
+    dim3 grid(n_heads / rep, n_rows, n_splits);
     const int chunks = head_dim / 8;
     // Eight (or sixteen) warps a block where that puts every (row, head) on the GPU at once with few
     // or no splits (batch 8 of 32 heads: 256 blocks of eight warps and no merge through scratch memory
@@ -413,16 +488,16 @@ TNX_EXPORT int tnx_attention_decode_append(const void* q, int q_stride, void* ca
     // the next power of two with idle lanes.  (5 pieces a lane for head sizes 80 and 160 was measured: 210
     // registers, one block an SM, and no faster than the idle lanes: 4.6 TB/s both.)
     switch (chunks) {
-        case 2: return launch_decode<2, 1>(warps, grid, stream, p);
-        case 3: case 4: return launch_decode<4, 1>(warps, grid, stream, p);
-        case 6: return launch_decode<2, 3>(warps, grid, stream, p);
-        case 5: case 7: case 8: return launch_decode<8, 1>(warps, grid, stream, p);
-        case 12: return launch_decode<4, 3>(warps, grid, stream, p);
-        case 24: return launch_decode<8, 3>(warps, grid, stream, p);
+        case 2: return launch_decode<2, 1>(warps, rep, grid, stream, p);
+        case 3: case 4: return launch_decode<4, 1>(warps, rep, grid, stream, p);
+        case 6: return launch_decode<2, 3>(warps, rep, grid, stream, p);
+        case 5: case 7: case 8: return launch_decode<8, 1>(warps, rep, grid, stream, p);
+        case 12: return launch_decode<4, 3>(warps, rep, grid, stream, p);
+        case 24: return launch_decode<8, 3>(warps, rep, grid, stream, p);
         default: break;
     }
-    if (chunks <= 16) return launch_decode<16, 1>(warps, grid, stream, p);
-    return launch_decode<32, 1>(warps, grid, stream, p);
+    if (chunks <= 16) return launch_decode<16, 1>(warps, rep, grid, stream, p);
+    return launch_decode<32, 1>(warps, rep, grid, stream, p);
 }
 
 TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cache, const int* block_tables,
@@ -432,7 +507,7 @@ TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cac
                                     float* scratch, int* counters, cudaStream_t stream) {
     return tnx_attention_decode_append(q, q_stride, const_cast<void*>(cache), block_tables, bt_stride, rows, token_request,
                                        positions, out, out_stride, n_rows, n_heads, n_kv_heads, head_dim, page_size, window,
-                                       scale, n_splits, pages_per_split, scratch, counters, nullptr, nullptr, 0, 4, stream);
+                                       scale, n_splits, pages_per_split, scratch, counters, nullptr, nullptr, 0, 4, 1, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------

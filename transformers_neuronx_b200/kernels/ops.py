@@ -607,12 +607,14 @@ def decode_attention_plan(pairs: int, sms: int, head_dim: int, max_pages: int):
 
 
 def attention_decode(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0, rows=None,
-                     n_rows=None, max_kv_len=None, n_splits=None, new_kv=None, warps=None):
+                     n_rows=None, max_kv_len=None, n_splits=None, new_kv=None, warps=None, grouped=None):
     """One query token per row over the paged 16-bit cache.  `rows` (int32) names the rows of q
     that are decode tokens (None: all); max_kv_len bounds their contexts (for the split plan).
     new_kv = (k, v), [rows of q, kv_heads * head_dim] bfloat16: the keys and values of the rows' own
     tokens, which the kernel then writes into their pages itself (no kv_append before it).
-    n_splits (with warps, 4 or 8 a block) forces a plan: a test hook."""
+    n_splits (with warps, 4 or 8 a block) forces a plan: a test hook.  grouped: with 2 or 4 query heads a key/value
+    head a block can take all query heads of a key/value head and read the head's pages once (None: where that pays;
+    True / False: a test hook)."""
     lib = _lib("attention_decode", cache, q, out)
     _need(cache, "cache", _H16, 5)
     N, width, q_stride = _rows_2d(q, "q")
@@ -629,8 +631,17 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
     st = _state(q.device)
     max_pages = max(1, -(-(int(max_kv_len) if max_kv_len is not None else block_tables.shape[1] * ps) // ps))
     forced_warps, warps = warps, 4
+    # with grouped key/value heads (2 or 4 query heads each) a block takes all query heads of a key/value head
+    # Measured (32 query heads of 128 on 8 key/value heads, contexts of 2,048): the grouped form wins from 64 rows on
+    # (a layer's step 1.58 against 1.77 ms at 64 rows, 2.44 against 2.78 at 128) and loses below (1.34 against 1.18 at 32:
+    # its blocks are a quarter as many, one an SM), so it runs once the (row, key/value head) pairs are three an SM.
+    heads_per_block = lib.tnx_attention_decode_heads_per_block(c_int(n_heads), c_int(n_kv), c_int(d))
+    if grouped is False or (grouped is None and R * n_kv < 3 * st["sms"]):
+        heads_per_block = 1
     if n_splits is None:
-        warps, n_splits = decode_attention_plan(R * n_heads, st["sms"], d, max_pages)
+        warps, n_splits = decode_attention_plan(R * n_heads // heads_per_block, st["sms"], d, max_pages)
+        if heads_per_block > 1 and warps == 16:
+            warps = 8                                           # their accumulators leave no registers for sixteen warps
         pps = -(-max_pages // n_splits)
         pps = -(-pps // warps) * warps
     else:                                                  # a test's own plan (warps: 4, 8 or 16 a block)
@@ -659,7 +670,7 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
         _p(rows), _p(token_request), _p(positions), _p(out), c_int(out_stride), c_int(R),
         c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0), c_float(scale),
         c_int(n_splits), c_int(pps), _p(scratch), _p(st.get("att_counters")), _p(k_new), _p(v_new), c_int(kv_stride),
-        c_int(warps), _stream()), "attention_decode")
+        c_int(warps), c_int(heads_per_block), _stream()), "attention_decode")
 
 
 ATTN_PREFILL_TILE = 128      # query rows of one work item of the prefill attention kernel
