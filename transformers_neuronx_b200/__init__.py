@@ -7,7 +7,7 @@ __version__ = "0.1.0"
 from .config.generation_config import (BlkSparseAttnConfig, ContinuousBatchingConfig, GenerationConfig, NeuronConfig,
                                        SlidingWindowAttnConfig, SparseAttnConfig)      # as `from transformers_neuronx import ...`
 
-_LAZY = {"OPTForSampling": ".opt.model", "OPTForGreedySearch": ".opt.model", "VononexForSampling": ".vononex.model",
+_LAZY = {"OPTForSampling": ".opt.model", "OPTForGreedySearch": ".opt.model", "VononexForSampling": ".vononex.model", "PifelixForSampling": ".pifelix.model",
          "NeuronAutoModelForCausalLM": ".modeling_auto", "HuggingFaceGenerationModelAdapter": ".generation_utils"}
 
 

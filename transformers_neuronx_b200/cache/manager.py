@@ -40,15 +40,18 @@ def _element_size(dtype) -> int:
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values of every position (window None) or of the last `window` positions, in the
-    engine's activation type: one tensor [pages, 2 (key, value), n_kv_heads, page_size, head_dim]."""
+    engine's activation type: one tensor [pages, 2 (key, value), n_kv_heads, page_size, head_dim].
+    `chunk`: queries read the keys of their own block of `chunk` positions only, so the pages of the blocks
+    before the running one are given back."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
     clear_on_admission = False
 
     @property
     def group_key(self):
-        return ("paged", self.window)
+        return ("paged", self.window) if self.chunk is None else ("paged", self.window, self.chunk)
 
     def make_storage(self, page_size, num_pages, max_slots, act_dtype, device):
         import torch
@@ -62,8 +65,8 @@ class PagedKVNeed:
 
 @dataclass(frozen=True)
 class FixedStateNeed:
-    """State of fixed size per request, e.g. of a recurrent mixer: shape and dtype name; one tensor
-    [slots, *shape].  A request that takes a slot finds its row zeroed."""
+    """State of fixed size per request, e.g. of a recurrent mixer: shape and dtype name ("activation": the
+    engine's activation type); one tensor [slots, *shape].  A request that takes a slot finds its row zeroed."""
     shape: Tuple[int, ...]
     dtype: str = "float32"
     clear_on_admission = True
@@ -74,7 +77,8 @@ class FixedStateNeed:
 
     def make_storage(self, page_size, num_pages, max_slots, act_dtype, device):
         import torch
-        return torch.zeros((max_slots,) + tuple(self.shape), dtype=getattr(torch, self.dtype), device=device)
+        dtype = act_dtype if self.dtype == "activation" else getattr(torch, self.dtype)
+        return torch.zeros((max_slots,) + tuple(self.shape), dtype=dtype, device=device)
 
 
 @dataclass
@@ -82,6 +86,12 @@ class GroupInfo:
     key: tuple
     cache_ids: List[int]
     window: Optional[int] = None
+    chunk: Optional[int] = None
+
+    @property
+    def releases(self) -> bool:
+        """Whether pages go back to the pool while their request still runs."""
+        return self.window is not None or self.chunk is not None
 
     @property
     def paged(self) -> bool:
@@ -98,7 +108,8 @@ def group_needs(needs: Dict[int, object]) -> List[GroupInfo]:
             continue
         k = need.group_key
         if k not in groups:
-            groups[k] = GroupInfo(key=k, cache_ids=[], window=getattr(need, "window", None))
+            groups[k] = GroupInfo(key=k, cache_ids=[], window=getattr(need, "window", None),
+                                  chunk=getattr(need, "chunk", None))
         groups[k].cache_ids.append(cid)
     return list(groups.values())
 
@@ -138,9 +149,11 @@ class CacheManager:
 
     def _first_needed_block(self, g: GroupInfo, length: int) -> int:
         """First block that a query at position >= length still reads."""
-        if g.window is None:
-            return 0
-        first_pos = max(0, length - g.window + 1)
+        first_pos = 0
+        if g.window is not None:
+            first_pos = max(0, length - g.window + 1)
+        if g.chunk is not None:
+            first_pos = max(first_pos, length // g.chunk * g.chunk)
         return first_pos // self.page_size
 
     def pages_needed(self, rid, n_new: int) -> List[int]:

@@ -32,7 +32,7 @@ struct DecodeParams {
     const int* positions;
     h16* out; int out_stride;
     int n_heads, n_kv_heads, head_dim;
-    int window;
+    int window;                      // the mask rule of common.cuh: first_visible_key
     float scale;
     int n_splits, pages_per_split;
     float* scratch;                  // [rows][heads][splits][head_dim + 2]
@@ -85,7 +85,7 @@ attention_decode_kernel(const DecodeParams p) {
             q_raw[x][e] = dim_ok ? *(const uint4*)(p.q + (size_t)row * p.q_stride + (size_t)(h0 + x) * d + (e * LPK + sub) * 8) : make_uint4(0, 0, 0, 0);
     if (req < 0) return;                                        // a padded row of a captured batch
     const int kv_len = pos + 1;
-    const int first_key = (p.window > 0 && kv_len > p.window) ? kv_len - p.window : 0;
+    const int first_key = first_visible_key(pos, p.window);
     const int kvh = h0 / (p.n_heads / p.n_kv_heads);
     const int* bt = p.block_tables + (size_t)req * p.bt_stride;
 

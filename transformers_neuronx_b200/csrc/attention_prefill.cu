@@ -115,8 +115,8 @@ attention_prefill_kernel(const PrefillParams p) {
     const int r_lo = warp * 16 + (lane >> 2);                // this thread's two rows within the tile
     const int qpos_lo = pos0 + r_lo, qpos_hi = qpos_lo + 8;
 
-    int key_begin = 0;
-    if (p.window > 0) key_begin = max(0, pos0 - p.window + 1) / BKV * BKV;
+    const int key_begin = first_visible_key(pos0, p.window) / BKV * BKV;     // p.window: the mask rule of common.cuh
+    const int first_lo = first_visible_key(qpos_lo, p.window), first_hi = first_visible_key(qpos_hi, p.window);
     const size_t head_block = (size_t)PAGE * d;
 
     auto load_tile = [&](int k0, int buf) {
@@ -174,7 +174,7 @@ attention_prefill_kernel(const PrefillParams p) {
         // position of this warp's rows (or fall partly behind the window) need the mask.
         const int warp_pos_lo = pos0 + warp * 16, warp_pos_hi = warp_pos_lo + 15;
         bool need_mask = k0 + BKV - 1 > warp_pos_lo;
-        if (p.window > 0) need_mask = need_mask || (k0 <= warp_pos_hi - p.window);
+        if (p.window != 0) need_mask = need_mask || k0 < first_visible_key(warp_pos_hi, p.window);
         if (need_mask) {
 #pragma unroll
             for (int nt = 0; nt < BKV / 8; ++nt) {
@@ -182,8 +182,7 @@ attention_prefill_kernel(const PrefillParams p) {
                 for (int e = 0; e < 4; ++e) {
                     const int key = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int qp = (e < 2) ? qpos_lo : qpos_hi;
-                    bool ok = key <= qp;
-                    if (p.window > 0) ok = ok && key > qp - p.window;
+                    const bool ok = key <= qp && key >= ((e < 2) ? first_lo : first_hi);
                     if (!ok) s[nt][e] = -INFINITY;
                 }
             }

@@ -145,8 +145,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int* bt = p.block_tables + (size_t)req * p.bt_stride;
     const int pos0 = ctx + q0, pos_last = pos0 + rows - 1;
     const int kv_total = ctx + ql;
-    int key_begin = 0;
-    if (p.window > 0) key_begin = max(0, pos0 - p.window + 1) / BKV * BKV;
+    const int key_begin = first_visible_key(pos0, p.window) / BKV * BKV;     // p.window: the mask rule of common.cuh
     const int n_tiles = (pos_last - key_begin) / BKV + 1;
 
     // K and V stages start as zeros: pages that do not exist are not loaded, and what a stage holds
@@ -285,6 +284,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int r = quad * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
         const int qpos = pos0 + r;
+        const int first_key = first_visible_key(qpos, p.window);
         float m_run = -INFINITY, l_run = 0.f;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int b = j & 1;
@@ -303,14 +303,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(raw0[i]); s[32 + i] = __uint_as_float(raw1[i]); }
             bool need_mask = k0 + BKV - 1 > qpos;
-            if (p.window > 0) need_mask = need_mask || (k0 <= qpos - p.window);
+            need_mask = need_mask || k0 < first_key;
             if (need_mask) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
                     const int key = k0 + i;
-                    bool keep = key <= qpos;
-                    if (p.window > 0) keep = keep && key > qpos - p.window;
-                    if (!keep) s[i] = -INFINITY;
+                    if (key > qpos || key < first_key) s[i] = -INFINITY;
                 }
             }
             // the row's maximum and sum as four chains each: no instruction waits for the one before it

@@ -2,7 +2,7 @@
 // path, and the path for head sizes that the tensor-core kernels refuse.
 //
 // One warp per (query token, head).  The query at position p of its request reads the keys at
-// positions max(0, p - window + 1) .. p, all of which are in the cache when the kernel runs (this
+// positions first_visible_key(p, window) .. p (a sliding window, a chunked mask or all: common.cuh), all of which are in the cache when the kernel runs (this
 // step's keys and values are written before it).  Keys are visited in ascending position, 32 at a
 // time, with an online softmax; the result for a token therefore does not depend on how the
 // request was cut into steps or on what else is in the batch.
@@ -42,7 +42,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
     float acc[MAX_DIMS_PER_LANE];
 #pragma unroll
     for (int i = 0; i < MAX_DIMS_PER_LANE; ++i) acc[i] = 0.f;
-    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first = first_visible_key(pos, window);
 
     for (int c0 = first; c0 <= pos; c0 += 32) {
         const int j = c0 + lane;

@@ -136,6 +136,16 @@ __device__ __forceinline__ float apply_activation(float v, int act) {
     return apply_activation_other(v, act);
 }
 
+// Which earlier keys a query reads, as one number (the `window` argument of the attention entry points):
+//   0: every key up to its own position;  w > 0: the last w of them (a sliding window);
+//   c < 0: those of its own block of -c positions, blocks counted from position 0 of the sequence (a chunked mask).
+// The first key a query at position `pos` reads; it never decreases as pos grows.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int mask) {
+    if (mask > 0) return pos - mask + 1 > 0 ? pos - mask + 1 : 0;
+    if (mask < 0) return pos / (-mask) * (-mask);
+    return 0;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

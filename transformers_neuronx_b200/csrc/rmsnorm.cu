@@ -45,6 +45,63 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, float x_scale, cons
     }
 }
 
+// The norm on a sublayer's output only:  out = x + add_scale * (delta / sqrt(mean(delta^2) + eps) * (w + w_offset)).
+// x is the 32-bit residual stream (out_f32 may be x itself), delta what the sublayer produced.
+template <typename TA, bool VEC>
+__global__ void rms_norm_add_kernel(const float* x, float add_scale, const float* __restrict__ delta,
+                                    const float* __restrict__ w, float w_offset, float eps, float* out_f32,
+                                    TA* __restrict__ out_act, int H) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t src = (size_t)blockIdx.x * H;
+    float s = 0.f;
+    if (VEC) {
+        const float4* ds = (const float4*)(delta + src);
+        for (int c = threadIdx.x; c < H / 4; c += blockDim.x) {
+            const float4 v = ds[c];
+            ((float4*)row)[c] = v;
+            s += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+        }
+    } else {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            const float v = delta[src + c];
+            row[c] = v;
+            s += v * v;
+        }
+    }
+    const float ms = block_sum(s, scratch) / (float)H;
+    const float rinv = 1.0f / sqrtf(ms + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float y = row[c] * rinv;
+        if (w) y *= (w[c] + w_offset);
+        y = fmaf(add_scale, y, x[src + c]);
+        if (out_f32) out_f32[src + c] = y;
+        if (out_act) out_act[src + c] = from_float<TA>(y);
+    }
+}
+
+TNX_EXPORT int tnx_rms_norm_add(const float* x, float add_scale, const float* delta, const float* w, float w_offset,
+                                float eps, float* out_f32, void* out_act, int n_rows, int H, int act_h16,
+                                cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (H <= 0 || smem > 200 * 1024 || !x || !delta) return TNX_ERR_UNSUPPORTED;
+    const bool vec = H % 4 == 0 && ((uintptr_t)delta % 16) == 0;
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+#define RMS_LAUNCH(TA, V)                                                                                              \
+    do {                                                                                                               \
+        if (smem + 1024 > 48 * 1024)                                                                                   \
+            cudaFuncSetAttribute(rms_norm_add_kernel<TA, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        return tnx_launch_ex(1, rms_norm_add_kernel<TA, V>, dim3(n_rows), dim3(threads), smem, stream, x, add_scale,   \
+                             delta, w, w_offset, eps, out_f32, (TA*)out_act, H);                                       \
+    } while (0)
+    if (act_h16) { if (vec) RMS_LAUNCH(h16, true); else RMS_LAUNCH(h16, false); }
+    if (vec) RMS_LAUNCH(float, true); else RMS_LAUNCH(float, false);
+#undef RMS_LAUNCH
+}
+
 TNX_EXPORT int tnx_rms_norm(const float* x, float x_scale, const float* delta, const int* rows, const float* w,
                             float w_offset, float eps, float* out_f32, void* out_act, int n_rows, int H, int act_h16,
                             cudaStream_t stream) {

@@ -373,7 +373,7 @@ class StepRunner:
         if n > filled:
             arr[filled:n] = table[filled:n]
             ent[1] = n
-        if self.cache.paged_groups[g].window is not None:       # released blocks turn to -1
+        if self.cache.paged_groups[g].releases:                 # released blocks turn to -1
             first = next((i for i, p in enumerate(table) if p >= 0), n)
             arr[:first] = -1
         return arr

@@ -48,6 +48,8 @@ SOURCES: Dict[str, str] = {
     "retention": "retention.cu",
     "mingru": "mingru.cu",
     "gated_act": "gated_act.cu",
+    "conv_qkv": "conv_qkv.cu",
+    "moe": "moe.cu",
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

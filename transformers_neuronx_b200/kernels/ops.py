@@ -121,8 +121,8 @@ def _rows_2d(t: torch.Tensor, name: str):
 
 
 # ---------------------------------------------------------------------------------------------
-def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_act):
-    """out[n] = (tok_table[ids[n]] or pre[n]) + pos_table[positions[n] + pos_offset]."""
+def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_act, tok_scale=1.0):
+    """out[n] = tok_scale * (tok_table[ids[n]] or pre[n]) + pos_table[positions[n] + pos_offset]."""
     lib = _lib("embedding", tok_table, pos_table, out_act)
     N = ids.shape[0]
     _need(ids, "ids", torch.int32, 1)
@@ -151,7 +151,7 @@ def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_ac
         _need(out_act, "out_act", _FLOATS, 2)
         act_bf16 = _is_h16(out_act)
     _check(lib.tnx_embed(_p(tok_table), _p(pre), _p(ids), _p(pos_table), _p(positions), c_int(pos_offset),
-                         _p(out_f32), _p(out_act), c_int(N), c_int(H), c_int(table_bf16), c_int(act_bf16),
+                         c_float(float(tok_scale)), _p(out_f32), _p(out_act), c_int(N), c_int(H), c_int(table_bf16), c_int(act_bf16),
                          _stream()), "embed")
 
 
@@ -263,7 +263,19 @@ def copy_rows(tensor, pairs):
     _check(lib.tnx_copy_rows(_p(tensor), _p(pairs), c_int(pairs.shape[0]), ctypes.c_longlong(row_bytes), _stream()), "copy_rows")
 
 
-def attention_simt(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0):
+def mask_rule(window=0, chunk=0) -> int:
+    """Which earlier keys a query reads, as the one number the attention kernels take (csrc/common.cuh:
+    first_visible_key): 0 all of them, w > 0 the last w (sliding window), -c those of the query's own block of c
+    positions, blocks counted from position 0 of the sequence (chunked mask)."""
+    window, chunk = int(window or 0), int(chunk or 0)
+    if window < 0 or chunk < 0:
+        raise KernelError("a window and a chunk are positive numbers of positions (0: none)")
+    if window and chunk:
+        raise KernelError("the attention kernels take a sliding window or a chunked mask, not both")
+    return -chunk if chunk else window
+
+
+def attention_simt(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0, chunk=0):
     """q: [N, n_heads * head_dim] view; out likewise; cache as in kv_append."""
     lib = _lib("attention_simt", cache, q, out)
     _need(cache, "cache", _FLOATS, 5)
@@ -277,7 +289,7 @@ def attention_simt(q, cache, block_tables, token_request, positions, out, n_head
     _need(positions, "positions", torch.int32, 1)
     _check(lib.tnx_attention_simt(_p(q), c_int(q_stride), _p(cache), _p(block_tables), c_int(block_tables.stride(0)),
                                   _p(token_request), _p(positions), _p(out), c_int(out_stride), c_int(N),
-                                  c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0),
+                                  c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(mask_rule(window, chunk)),
                                   c_float(scale), c_int(_is_h16(cache)), _stream()), "attention_simt")
 
 
@@ -607,7 +619,7 @@ def decode_attention_plan(pairs: int, sms: int, head_dim: int, max_pages: int):
 
 
 def attention_decode(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0, rows=None,
-                     n_rows=None, max_kv_len=None, n_splits=None, new_kv=None, warps=None, grouped=None):
+                     n_rows=None, max_kv_len=None, n_splits=None, new_kv=None, warps=None, grouped=None, chunk=0):
     """One query token per row over the paged 16-bit cache.  `rows` (int32) names the rows of q
     that are decode tokens (None: all); max_kv_len bounds their contexts (for the split plan).
     new_kv = (k, v), [rows of q, kv_heads * head_dim] bfloat16: the keys and values of the rows' own
@@ -668,7 +680,7 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
     _check(lib.tnx_attention_decode_append(
         _p(q), c_int(q_stride), _p(cache), _p(block_tables), c_int(block_tables.stride(0)),
         _p(rows), _p(token_request), _p(positions), _p(out), c_int(out_stride), c_int(R),
-        c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0), c_float(scale),
+        c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(mask_rule(window, chunk)), c_float(scale),
         c_int(n_splits), c_int(pps), _p(scratch), _p(st.get("att_counters")), _p(k_new), _p(v_new), c_int(kv_stride),
         c_int(warps), c_int(heads_per_block), _stream()), "attention_decode")
 
@@ -677,7 +689,7 @@ ATTN_PREFILL_TILE = 128      # query rows of one work item of the prefill attent
 
 
 def attention_prefill(q, cache, block_tables, tile_req, tile_q0, q_start, q_len, ctx_len, out, n_heads, scale,
-                      window=0, n_items=None):
+                      window=0, n_items=None, chunk=0):
     """Causal attention of prompt portions: work items (request, first row of an ATTN_PREFILL_TILE-row tile)."""
     lib = _lib("attention_prefill", cache, q, out)
     _need(cache, "cache", _H16, 5)
@@ -693,7 +705,7 @@ def attention_prefill(q, cache, block_tables, tile_req, tile_q0, q_start, q_len,
     _check(lib.tnx_attention_prefill(_p(q), c_int(q_stride), _p(cache), _p(block_tables), c_int(block_tables.stride(0)),
                                      _p(tile_req), _p(tile_q0), _p(q_start), _p(q_len), _p(ctx_len), _p(out),
                                      c_int(out_stride), c_int(n), c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps),
-                                     c_int(window or 0), c_float(scale), _stream()), "attention_prefill")
+                                     c_int(mask_rule(window, chunk)), c_float(scale), _stream()), "attention_prefill")
 
 
 def attention_prefill_tc_supported(q, cache, out) -> bool:
@@ -704,7 +716,7 @@ def attention_prefill_tc_supported(q, cache, out) -> bool:
 
 
 def attention_prefill_tc(q, cache, block_tables, tile_req, tile_q0, q_start, q_len, ctx_len, out, n_heads, scale,
-                         window=0, n_items=None):
+                         window=0, n_items=None, chunk=0):
     """attention_prefill on the tcgen05 tensor cores (head sizes 64 to 128 in steps of 16).  The cache must hold finite
     numbers in every row, written or not (CacheStorage allocates it zeroed)."""
     lib = _lib("attention_prefill_tc", cache, q, out)
@@ -722,11 +734,11 @@ def attention_prefill_tc(q, cache, block_tables, tile_req, tile_q0, q_start, q_l
     _check(lib.tnx_attention_prefill_tc(_p(q), c_int(q_stride), c_int(N), _p(cache), ctypes.c_longlong(n_pages * 2 * n_kv * ps),
                                         _p(block_tables), c_int(block_tables.stride(0)), _p(tile_req), _p(tile_q0),
                                         _p(q_start), _p(q_len), _p(ctx_len), _p(out), c_int(out_stride), c_int(n),
-                                        c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0),
+                                        c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(mask_rule(window, chunk)),
                                         c_float(scale), _p(st["err"]), _stream()), "attention_prefill_tc")
 
 
-def _attention_h16(ctx, group, q, cache, out, n_heads, scale, window, new_kv):
+def _attention_h16(ctx, group, q, cache, out, n_heads, scale, window, new_kv, chunk=0):
     if cache.shape[3] != 16 or q.stride(0) % 8 or q.data_ptr() % 16:
         return False
     bt = ctx.block_tables[group]
@@ -741,31 +753,32 @@ def _attention_h16(ctx, group, q, cache, out, n_heads, scale, window, new_kv):
     if ctx.n_prefill_tiles:
         prefill = attention_prefill_tc if attention_prefill_tc_supported(q, cache, out) else attention_prefill
         prefill(q, cache, bt, ctx.tile_req, ctx.tile_q0, ctx.q_start, ctx.q_len, ctx.ctx_len, out,
-                n_heads, scale, window, n_items=ctx.n_prefill_tiles)
+                n_heads, scale, window, n_items=ctx.n_prefill_tiles, chunk=chunk)
     if ctx.n_decode_rows:
         attention_decode(q, cache, bt, ctx.token_request, ctx.positions, out, n_heads, scale, window,
                          rows=None if ctx.decode_only else ctx.decode_rows, n_rows=ctx.n_decode_rows,
-                         max_kv_len=ctx.max_decode_ctx, new_kv=fused)
+                         max_kv_len=ctx.max_decode_ctx, new_kv=fused, chunk=chunk)
     return True
 
 
 _attention_impls["h16"] = _attention_h16
 
 
-def attention(ctx, group, q, cache, out, n_heads, scale, window=0, new_kv=None):
+def attention(ctx, group, q, cache, out, n_heads, scale, window=0, new_kv=None, chunk=0):
     """Attention of this step's queries over the cache of the running schedule entry.  32-bit
     caches, and head sizes or windows that the 16-bit kernels do not take, run on the CUDA-core
     kernel; a 16-bit cache runs the prefill kernel for requests with several rows and the split
     decode kernel for requests with one.  new_kv = (k, v, slot_mapping): the keys and values of
     this step's tokens, not yet in the cache; they are appended here, by kv_append or (a step of
-    decode tokens only, 16-bit) by the decode kernel itself."""
+    decode tokens only, 16-bit) by the decode kernel itself; None: the cache holds them already (a mixer that
+    reads another mixer's pages).  window / chunk: see mask_rule."""
     impl = _attention_impls.get("h16") if cache.dtype in _H16 else None
-    if impl is not None and impl(ctx, group, q, cache, out, n_heads, scale, window, new_kv):
+    if impl is not None and impl(ctx, group, q, cache, out, n_heads, scale, window, new_kv, chunk):
         return
     if new_kv is not None:
         kv_append(new_kv[0], new_kv[1], new_kv[2], cache, ctx.page_size)
     attention_simt(q, cache, ctx.block_tables[group], ctx.token_request, ctx.positions, out, n_heads, scale,
-                   window)
+                   window, chunk)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -801,6 +814,121 @@ def rms_norm(x, weight, eps, out_f32=None, out_act=None, rows=None, x_scale=1.0,
     _check(lib.tnx_rms_norm(_p(x), c_float(x_scale), _p(delta), _p(rows), _p(weight), c_float(weight_offset),
                             c_float(eps), _p(out_f32), _p(out_act), c_int(n_rows), c_int(H),
                             c_int(_is_h16(out_act) if out_act is not None else 0), _stream()), "rms_norm")
+
+
+def rms_norm_add(x, add_scale, delta, weight, eps, out_f32=None, out_act=None, weight_offset=0.0):
+    """x + add_scale * (delta / rms(delta) * (weight + weight_offset)): the norm on a sublayer's output alone, added to
+    the 32-bit stream x.  out_f32 may be x itself."""
+    lib = _lib("rmsnorm", out_act)
+    _need(x, "x", torch.float32, 2)
+    _need(delta, "delta", torch.float32, 2)
+    if tuple(delta.shape) != tuple(x.shape):
+        raise KernelError("delta must have the shape of x")
+    N, H = x.shape
+    _f32_vec(weight, "weight", H)
+    for t, nm in ((out_f32, "out_f32"), (out_act, "out_act")):
+        if t is not None:
+            _need(t, nm, torch.float32 if nm == "out_f32" else _FLOATS, 2)
+            if tuple(t.shape) != (N, H):
+                raise KernelError(f"{nm} has shape {tuple(t.shape)}, needs [{N}, {H}]")
+    _check(lib.tnx_rms_norm_add(_p(x), c_float(add_scale), _p(delta), _p(weight), c_float(weight_offset), c_float(eps),
+                                _p(out_f32), _p(out_act), c_int(N), c_int(H),
+                                c_int(_is_h16(out_act) if out_act is not None else 0), _stream()), "rms_norm_add")
+
+
+def conv_qkv_prep(proj, col0, conv_w, taps, state, ctx, q_norm, k_norm, eps, inv_freq, rot_dims, interleaved, magnitude,
+                  q_out, k_out, v_out, n_heads, n_kv_heads, k_dim, v_dim, pad_dim):
+    """From one product's output `proj` [N, *] (from column col0 on: queries, then keys and values unless n_kv_heads is
+    0): each channel's short causal convolution over the request's positions (conv_w [channels, taps] 32-bit; None:
+    none), whose past comes from this step's rows or from `state` [slots, taps - 1, channels] (brought up to date here);
+    queries and keys normalised per head (q_norm, k_norm [k_dim]; None: not), then turned by position on their first
+    rot_dims dims (interleaved pairs or halves; sines and cosines times `magnitude`); written with pad_dim dims a head."""
+    lib = _lib("conv_qkv", proj, q_out)
+    _need(proj, "proj", _FLOATS, None, contiguous=False)
+    N, width, ld = _rows_2d(proj, "proj")
+    H, G, dk, dv, D = n_heads, n_kv_heads, k_dim, v_dim, pad_dim
+    channels = H * dk + G * (dk + dv)
+    if col0 < 0 or col0 + channels > width:
+        raise KernelError("the projection is narrower than its q/k/v columns")
+    outs = [(q_out, "q_out", H * D)] + ([(k_out, "k_out", G * D), (v_out, "v_out", G * D)] if G else [])
+    for t, nm, w in outs:
+        _need(t, nm, proj.dtype, 2)
+        if tuple(t.shape) != (N, w):
+            raise KernelError(f"{nm} must be [{N}, {w}]")
+    _f32_vec(q_norm, "q_norm", dk); _f32_vec(k_norm, "k_norm", dk)
+    _f32_vec(inv_freq, "inv_freq", rot_dims // 2 if rot_dims else None)
+    keep = 0
+    if conv_w is not None:
+        _need(conv_w, "conv_w", torch.float32, 2)
+        if tuple(conv_w.shape) != (channels, taps):
+            raise KernelError(f"conv_w must be [{channels}, {taps}]")
+        keep = taps - 1
+    if keep:
+        _need(state, "state", proj.dtype, 3)
+        if tuple(state.shape[1:]) != (keep, channels):
+            raise KernelError(f"state must be [slots, {keep}, {channels}]")
+    for t, nm in ((ctx.token_request, "token_request"), (ctx.positions, "positions"), (ctx.q_start, "q_start"),
+                  (ctx.q_len, "q_len"), (ctx.state_slots, "state_slots")):
+        _need(t, nm, torch.int32, 1)
+    R = ctx.q_len.shape[0]
+    update = 0 if (ctx.decode_only or not keep) else 1
+    _check(lib.tnx_conv_qkv_prep(_p(proj), c_int(ld), c_int(col0), _p(conv_w), c_int(taps if conv_w is not None else 1),
+                                 _p(state if keep else None), _p(ctx.token_request), _p(ctx.positions), _p(ctx.q_start),
+                                 _p(ctx.q_len), _p(ctx.state_slots), c_int(R), c_int(update), _p(q_norm), _p(k_norm),
+                                 c_float(eps), _p(inv_freq), c_int(rot_dims if inv_freq is not None else 0),
+                                 c_int(1 if interleaved else 0), c_float(magnitude), _p(q_out), _p(k_out if G else None),
+                                 _p(v_out if G else None), c_int(N), c_int(H), c_int(G), c_int(dk), c_int(dv), c_int(D),
+                                 c_int(_is_h16(proj)), _stream()), "conv_qkv_prep")
+    add_launches(update)
+
+
+def moe_route(h, router, token_request, ids, weights, top, softmax_scores=False, renormalize=False):
+    """For every row of h [N, W]: the `top` experts with the largest scores (sigmoid, or softmax, of the 32-bit product
+    with router [E, W]) into ids [N, top] (int32; -1 for a padded row) and their scores into weights [N, top]."""
+    lib = _lib("moe", h, router)
+    _need(h, "h", _FLOATS, None, contiguous=False)
+    N, W, ld = _rows_2d(h, "h")
+    _need(router, "router", _FLOATS, 2)
+    E = router.shape[0]
+    if router.shape[1] != W:
+        raise KernelError("the router's rows must be as long as h's")
+    _need(token_request, "token_request", torch.int32, 1)
+    _need(ids, "ids", torch.int32, 2); _need(weights, "weights", torch.float32, 2)
+    if tuple(ids.shape) != (N, top) or tuple(weights.shape) != (N, top):
+        raise KernelError(f"ids and weights must be [{N}, {top}]")
+    _check(lib.tnx_moe_route(_p(h), c_int(ld), _p(router), _p(token_request), _p(ids), _p(weights), c_int(N), c_int(W),
+                             c_int(E), c_int(top), c_int(1 if softmax_scores else 0), c_int(1 if renormalize else 0),
+                             c_int(_is_h16(h)), c_int(_is_h16(router)), _stream()), "moe_route")
+
+
+def moe_experts(h, gate_up, down, ids, weights, y, out, gate_max, up_min, up_max, alpha, up_shift, weight_on_input=True,
+                accumulate=False):
+    """The chosen experts of every row, each expert's matrices streamed once per row: gate_up [E, 2F, W] (gate rows,
+    then up rows), down [E, W, F]; y [N * top, F] scratch in h's type; out 32-bit [N, W], written or added to."""
+    lib = _lib("moe", h, gate_up)
+    _need(h, "h", _FLOATS, None, contiguous=False)
+    N, W, ld = _rows_2d(h, "h")
+    _need(gate_up, "gate_up", _FLOATS, 3); _need(down, "down", gate_up.dtype, 3)
+    E, F2, Wg = gate_up.shape
+    F = F2 // 2
+    if Wg != W or F2 % 2 or tuple(down.shape) != (E, W, F):
+        raise KernelError(f"gate_up must be [E, 2F, {W}] and down [E, {W}, F]")
+    top = ids.shape[1]
+    _need(ids, "ids", torch.int32, 2); _need(weights, "weights", torch.float32, 2)
+    _need(y, "y", h.dtype, 2); _need(out, "out", torch.float32, 2)
+    if tuple(ids.shape) != (N, top) or tuple(weights.shape) != (N, top) or tuple(y.shape) != (N * top, F) \
+            or tuple(out.shape) != (N, W):
+        raise KernelError("ids, weights, y or out do not fit the rows and experts")
+    _check(lib.tnx_moe_experts(_p(h), c_int(ld), _p(gate_up), _p(down), _p(ids), _p(weights), _p(y), _p(out), c_int(N),
+                               c_int(W), c_int(F), c_int(top), c_float(gate_max), c_float(up_min), c_float(up_max),
+                               c_float(alpha), c_float(up_shift), c_int(1 if weight_on_input else 0),
+                               c_int(1 if accumulate else 0), c_int(_is_h16(h)), c_int(_is_h16(gate_up)), _stream()),
+           "moe_experts")
+    add_launches(1)
+
+
+def moe_grouped_supported(h, gate_up, down) -> bool:
+    return False
 
 
 def rotary_qkv_prep(proj, q_off, k_off, v_off, token_request, positions, q_weight, k_weight, eps, head_scale,

@@ -4,5 +4,6 @@ from .registry import (build_block, build_part, register_block, register_feed_fo
                        register_norm, register_position)
 from .linear import Linear, linear_forward
 from . import norm, position, attention, feedforward, block, embedding   # register the built-in kinds
-from . import rotary_attention, retention, mingru, parallel   # noqa: F401  more built-in mixers
+from . import rotary_attention, retention, mingru, parallel, conv_attention   # noqa: F401  more built-in mixers
+from . import moe   # noqa: F401  the feed-forward of routed experts
 from .embedding import Embedding, Head

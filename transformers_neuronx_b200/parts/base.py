@@ -87,6 +87,13 @@ class StepContext:
     def cache_group(self, sub=None) -> int:
         return self.storage.group_of(self.cache_id if sub is None else (self.cache_id, sub))
 
+    # what the mixer of ANOTHER schedule entry owns (a mixer that reads the pages an earlier one wrote in this step)
+    def cache_of(self, cache_id, sub=None) -> torch.Tensor:
+        return self.storage.tensor(cache_id if sub is None else (cache_id, sub))
+
+    def cache_group_of(self, cache_id, sub=None) -> int:
+        return self.storage.group_of(cache_id if sub is None else (cache_id, sub))
+
 
 class Part:
     libraries: Sequence[str] = ()

@@ -9,6 +9,11 @@ post_norm_scaled:                                         x = norm1(a x + mixer(
     sublayer's result goes into a 32-bit buffer of its own and the norm's kernel forms the sum
     (Norm.forward_sum), so the stream is read and written once per sublayer.
 
+output_norm:                                              x = x + m norm1(mixer(x)); x = x + m norm2(ff(x))
+    with m = the layer's residual_scale: the norm sits on the sublayer's output only and the sublayers read x
+    itself.  The sublayer's result goes into a 32-bit buffer and the norm's kernel adds it to the stream
+    (Norm.forward_add); a layer may have no feed-forward.
+
 `x` is the 32-bit residual stream and is updated in place; `x_act` is its copy in the activation
 type, which a block that feeds x itself into a matrix product needs on entry
 (``needs_act_input``) and keeps current (``keeps_act_current``).
@@ -97,6 +102,28 @@ class ScaledPostNormBlock:
             self.norm2.forward_sum(ctx, x, self.residual_scale, out, out_f32=x, out_act=x_act)
 
 
+class OutputNormBlock(ScaledPostNormBlock):
+    """x <- x + residual_scale * norm(sublayer(x)): the sublayers read the stream itself (its copy in the
+    activation type), only what they produce is normalised."""
+
+    def __init__(self, norm1, mixer, norm2, feed_forward, layer_spec=None):
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        self.residual_scale = float(getattr(layer_spec, "residual_scale", 1.0))
+        for n in (norm1, norm2 if feed_forward is not None else None):
+            if n is None or not hasattr(n, "forward_add"):
+                raise ValueError(f"an output_norm block needs norms that add a normalised sublayer output to the stream; "
+                                 f"{type(n).__name__} does not")
+
+    def forward(self, ctx, x, x_act):
+        out = ctx.scratch(x.shape[0], x.shape[1], x.dtype)
+        self._run(ctx, self.mixer, x_act, out)
+        self.norm1.forward_add(ctx, x, self.residual_scale, out, out_f32=x, out_act=x_act)
+        if self.feed_forward is not None:
+            self._run(ctx, self.feed_forward, x_act, out)
+            self.norm2.forward_add(ctx, x, self.residual_scale, out, out_f32=x, out_act=x_act)
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("output_norm", OutputNormBlock)
 register_block("post_norm_scaled", ScaledPostNormBlock)
 register_block("post_norm", PostNormBlock)

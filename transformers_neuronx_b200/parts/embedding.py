@@ -69,7 +69,7 @@ class Embedding(Part):
             pre = ctx.empty(ctx.n_tokens, x.shape[1], torch.float32)
             self.project_in.forward(e, pre)
             tok = None
-        ops.embed(tok, pre, ctx.token_ids, pos_table, ctx.positions, offset, x, x_act)
+        ops.embed(tok, pre, ctx.token_ids, pos_table, ctx.positions, offset, x, x_act, tok_scale=self.spec.scale)
         if self.position is not None and table_pos is None:
             self.position.embed(ctx, x)
             if x_act is not None:

@@ -1,0 +1,92 @@
+"""A feed-forward of routed experts: each token runs `top` of `n_experts` small gated feed-forwards.
+
+  z = W_router h (32-bit sums), s = sigmoid(z) or softmax(z); the `top` largest scores choose the experts
+  w_j = s[e_j], or s[e_j] / sum_j s[e_j] with `renormalize`
+  expert(x) = W_down (g * sigmoid(act_alpha g) * (u + up_shift)),  g = min(W_gate x, gate_limit),
+              u = clamp(W_up x, -up_limit, up_limit)
+  result = sum_j expert_{e_j}(w_j h)  (weight_on_input)   or   sum_j w_j expert_{e_j}(h)
+
+The experts' matrices are kept stacked, [E, 2 ff, hidden] (gate rows, then up rows) and [E, hidden, ff], in the type
+they are stored in.  A step routes on the device (no read on the host: the part is graph-safe) and then takes one of
+two forms: few tokens stream the chosen experts' matrices once per token (csrc/moe.cu); many tokens are sorted by
+expert and run as grouped products on the tensor cores (csrc/moe_grouped.cu).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import TensorSpec
+from .base import FeedForward, weight_to_device
+from .registry import register_feed_forward
+from .spec import RoutedFeedForwardSpec
+
+
+class RoutedExperts(FeedForward):
+    graph_safe = True
+    can_overwrite = True
+    libraries = ("moe",)
+    GROUPED_FROM = 64        # rows from which the grouped tensor-core form runs (16-bit engines)
+
+    def __init__(self, spec: RoutedFeedForwardSpec):
+        s = self.spec = spec
+        if not (1 <= s.top <= s.n_experts) or len(s.experts) != s.n_experts:
+            raise ValueError(f"{s.top} of {s.n_experts} experts ({len(s.experts)} listed) is not a choice")
+        if s.top > 8 or s.n_experts > 1024:
+            raise ValueError("the routing kernel takes up to 8 chosen of up to 1024 experts")
+        if s.scores not in ("sigmoid", "softmax"):
+            raise ValueError(f"unknown scores {s.scores!r}: sigmoid or softmax")
+        self.router = self.gate_up = self.down = None
+
+    def tensor_specs(self):
+        s = self.spec
+        out = [TensorSpec(s.router, (s.n_experts, s.hidden), "matrix")]
+        for e in s.experts:
+            out += [TensorSpec(e.gate, (s.ff, s.hidden), "matrix"), TensorSpec(e.up, (s.ff, s.hidden), "matrix"),
+                    TensorSpec(e.down, (s.hidden, s.ff), "matrix")]
+        return out
+
+    def load(self, tensors, device, act_dtype):
+        s = self.spec
+        self.router = weight_to_device(tensors[s.router], device, act_dtype, s.router)
+        first = weight_to_device(tensors[s.experts[0].gate], device, act_dtype, s.experts[0].gate)
+        self.gate_up = torch.empty((s.n_experts, 2 * s.ff, s.hidden), dtype=first.dtype, device=device)
+        self.down = torch.empty((s.n_experts, s.hidden, s.ff), dtype=first.dtype, device=device)
+        for i, e in enumerate(s.experts):
+            for name, dst in ((e.gate, self.gate_up[i, :s.ff]), (e.up, self.gate_up[i, s.ff:]), (e.down, self.down[i])):
+                w = weight_to_device(tensors[name], device, act_dtype, name)
+                if w.dtype != first.dtype:
+                    raise ValueError(f"{name} is stored as {w.dtype}, the other experts' matrices as {first.dtype}")
+                dst.copy_(w)
+
+    def parameter_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.router, self.gate_up, self.down))
+
+    def step_bytes(self, n_tokens: int) -> int:
+        """Bytes of weights a step of n_tokens reads at most (every expert once it is chosen by somebody)."""
+        s = self.spec
+        used = min(s.n_experts, n_tokens * s.top)
+        per = (self.gate_up[0].numel() + self.down[0].numel()) * self.gate_up.element_size()
+        return self.router.numel() * self.router.element_size() + used * per
+
+    def forward(self, ctx, h, out, accumulate=True):
+        s, N = self.spec, h.shape[0]
+        ids = ctx.scratch(N, s.top, torch.int32)
+        weights = ctx.scratch(N, s.top, torch.float32)
+        ops.moe_route(h, self.router, ctx.token_request, ids, weights, s.top, softmax_scores=s.scores == "softmax",
+                      renormalize=s.renormalize)
+        inf = math.inf
+        limits = (s.gate_limit if s.gate_limit is not None else inf, -s.up_limit if s.up_limit is not None else -inf,
+                  s.up_limit if s.up_limit is not None else inf)
+        if N >= self.GROUPED_FROM and ops.moe_grouped_supported(h, self.gate_up, self.down):
+            ops.moe_grouped(ctx, h, self.gate_up, self.down, ids, weights, out, *limits, s.act_alpha, s.up_shift,
+                            weight_on_input=s.weight_on_input, accumulate=accumulate)
+            return
+        y = ctx.scratch(N * s.top, s.ff)
+        ops.moe_experts(h, self.gate_up, self.down, ids, weights, y, out, *limits, s.act_alpha, s.up_shift,
+                        weight_on_input=s.weight_on_input, accumulate=accumulate)
+
+
+register_feed_forward("routed_experts", RoutedExperts)

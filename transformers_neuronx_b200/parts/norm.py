@@ -1,7 +1,8 @@
 """Norms over the hidden axis.
 
 RMS norm: y / sqrt(mean(y^2) + eps) * (weight + weight_offset), in 32-bit; it can normalise a sum
-y = x_scale * x + delta in the same kernel, which is what a post-norm block with a scaled residual asks for.
+y = x_scale * x + delta in the same kernel, which is what a post-norm block with a scaled residual asks for,
+or normalise a sublayer's output alone and add it to the stream (x + add_scale * norm(delta)).
 
 LayerNorm as the reference computes it: statistics and affine in 32-bit over the hidden axis
 (src/transformers_neuronx/hlo.py:84-105), with eps, scale and shift as parameters of the part."""
@@ -77,6 +78,11 @@ class RMSNorm(Norm):
         """norm(x_scale * x + delta) in one kernel; out_f32 may be x."""
         ops.rms_norm(x, self.weight, self.spec.eps, out_f32=out_f32, out_act=out_act, x_scale=x_scale, delta=delta,
                      weight_offset=self.spec.weight_offset)
+
+    def forward_add(self, ctx, x, add_scale, delta, out_f32=None, out_act=None):
+        """x + add_scale * norm(delta) in one kernel (the norm on a sublayer's output alone); out_f32 may be x."""
+        ops.rms_norm_add(x, add_scale, delta, self.weight, self.spec.eps, out_f32=out_f32, out_act=out_act,
+                         weight_offset=self.spec.weight_offset)
 
 
 register_norm("layer_norm", LayerNorm)

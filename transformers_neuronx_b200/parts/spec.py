@@ -31,11 +31,25 @@ class NormSpec:
 
 
 @dataclass(frozen=True)
+class FrequencyRampSpec:
+    """Stretching of a rotation's frequencies for contexts longer than the `original` one ("YaRN"): with
+    turns(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(turns(fast)), 0),
+    hi = min(ceil(turns(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns by
+    f_i / factor * ramp_i + f_i * (1 - ramp_i), and sines and cosines are multiplied by 0.1 ln(factor) + 1."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
 class RotarySpec:
-    """Rotation of pairs of dims by position: over the first `dims` dims of a head, dim i is paired with
-    dim i + dims/2 and turned by position * base^(-2i/dims)."""
+    """Rotation of pairs of dims by position over the first `dims` dims of a head: pair i turns by
+    position * base^(-2i/dims).  Pair i is (dim i, dim i + dims/2), or with `interleaved` (dim 2i, dim 2i + 1)."""
     dims: int
     base: float
+    interleaved: bool = False
+    scaling: Optional[FrequencyRampSpec] = None
 
 
 @dataclass(frozen=True)
@@ -90,6 +104,39 @@ class RotaryAttentionSpec:
 
 
 @dataclass(frozen=True)
+class ConvAttentionSpec:
+    """Softmax attention over the paged cache whose projections (with bias) pass through a short causal convolution
+    over time, channel by channel, before queries and keys are normalised per head (one weight vector of k_dim for
+    all heads) and rotated.  The mask is causal, and a sliding window or chunked (a query reads the keys of its own
+    block of `chunk` positions).  With `kv_source` the mixer has no keys and values of its own: it reads the pages
+    of the mixer whose schedule entry has that cache number (which ran earlier in the step), with its own queries
+    and mask."""
+    kind: str                        # 'conv_attention'
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    k_dim: int
+    v_dim: int
+    scale: float
+    q: LinearSpec = None
+    k: Optional[LinearSpec] = None
+    v: Optional[LinearSpec] = None
+    out: LinearSpec = None
+    conv_taps: int = 0               # taps of the convolution; 0: none
+    q_conv: Optional[str] = None     # tensor [n_heads * k_dim, conv_taps]; tap j weighs the value conv_taps - 1 - j back
+    k_conv: Optional[str] = None
+    v_conv: Optional[str] = None
+    q_norm: Optional[str] = None     # tensor [k_dim]: RMS norm of every query head, before rotation
+    k_norm: Optional[str] = None
+    norm_eps: float = 1e-6
+    rotary: Optional[RotarySpec] = None
+    window: Optional[int] = None
+    chunk: Optional[int] = None
+    kv_source: Optional[int] = None
+    keep_all_pages: bool = False     # another mixer reads these pages with another mask: none is given back early
+
+
+@dataclass(frozen=True)
 class RetentionSpec:
     """Linear attention with a fixed decay per head: S <- decay S + k v^T, o = S^T q; each head's o divided by
     its root mean square, gated by silu of a projection, then the output projection."""
@@ -139,6 +186,35 @@ class GatedFeedForwardSpec:
 
 
 @dataclass(frozen=True)
+class ExpertSpec:
+    gate: str                        # tensor names, [ff, hidden], [ff, hidden], [hidden, ff]; no biases
+    up: str
+    down: str
+
+
+@dataclass(frozen=True)
+class RoutedFeedForwardSpec:
+    """Experts chosen per token by a router: scores = sigmoid (or softmax) of router(h) in 32-bit, the `top` largest
+    choose, their scores are the weights (divided by their sum with `renormalize`).  An expert computes
+    down(g * sigmoid(act_alpha g) * (u + up_shift)) with g = min(gate(x), gate_limit) and u = clamp(up(x), +-up_limit);
+    the weight multiplies the expert's input x = w h (`weight_on_input`) or its output."""
+    kind: str                        # 'routed_experts'
+    hidden: int
+    ff: int
+    n_experts: int
+    top: int
+    router: str = None               # tensor [n_experts, hidden]
+    experts: Tuple[ExpertSpec, ...] = ()
+    scores: str = "sigmoid"          # 'sigmoid' | 'softmax'
+    renormalize: bool = False
+    weight_on_input: bool = True
+    gate_limit: Optional[float] = None
+    up_limit: Optional[float] = None
+    act_alpha: float = 1.702
+    up_shift: float = 1.0
+
+
+@dataclass(frozen=True)
 class DenseFeedForwardSpec:
     kind: str                        # 'dense'
     fc1: LinearSpec = None
@@ -148,12 +224,13 @@ class DenseFeedForwardSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    block: str                       # 'pre_norm' | 'post_norm' | 'post_norm_scaled' | a registered kind
+    block: str                       # 'pre_norm' | 'post_norm' | 'post_norm_scaled' | 'output_norm' | a registered kind
     norm1: Any = None
     mixer: Any = None
     norm2: Any = None
     feed_forward: Any = None         # None: the layer has no feed-forward (and no second norm)
-    residual_scale: float = 1.0      # 'post_norm_scaled': x <- norm(residual_scale * x + sublayer(x))
+    residual_scale: float = 1.0      # 'post_norm_scaled': x <- norm(residual_scale * x + sublayer(x));
+                                     # 'output_norm': x <- x + residual_scale * norm(sublayer(x))
 
 
 @dataclass(frozen=True)
@@ -163,6 +240,7 @@ class EmbeddingSpec:
     dim: int = 0
     project_in: Optional[LinearSpec] = None
     position: Optional[PositionSpec] = None   # an encoding added to the hidden state, if any
+    scale: float = 1.0               # the token's row is multiplied by it (in 32-bit) as it enters the stream
 
 
 @dataclass(frozen=True)
