@@ -16,7 +16,9 @@ src/transformers_neuronx/generation_demo.py:157-163), and the two further worklo
 OPT-30B sizes decoding at batch 16, and OPT-13B sizes serving 32 requests with a 512-token budget.
 
 `--workload vononex` (a line of its own, not part of the default one): prefill and decode of the Vononex decoder at
-two widths beside OPT at the same width, with every kernel family's time.
+two widths beside OPT at the same width, with every kernel family's time.  `--workload pifelix`: the same for the
+Pifelix decoder (attention behind convolved projections under a chunked mask, two of four layers reading another
+layer's pages, eight experts of which a token runs two).
 """
 from __future__ import annotations
 
@@ -388,12 +390,31 @@ def vononex_config(size):
             "init_std": 0.02, "max_positions": CONTEXT, "layers": [par if t == "parallel" else gru for t in VONONEX_LAYERS]}
 
 
-def build_vononex(size, dtype="bfloat16"):
+# ---- the Pifelix decoder beside OPT at equal sizes ---------------------------------------------------
+# Heads of 128 dims on a quarter as many key/value heads, three taps, a chunk as long as the bench's context (every
+# key is read, as in OPT beside it), eight experts of which a token runs two; an expert's inner width makes the two
+# chosen experts' three matrices as large as OPT's two (8 W^2 parameters a token).  Layers 2 and 3 read layer 1's pages.
+PIFELIX_SIZES = {"2048": dict(width=2048, heads=16, kv=4, ff=2816), "4096": dict(width=4096, heads=32, kv=8, ff=5504)}
+PIFELIX_LAYERS = ("own", "own", "reads 1", "reads 1")
+PIFELIX_EXPERTS, PIFELIX_TOP = 8, 2
+
+
+def pifelix_config(size):
+    z = PIFELIX_SIZES[size]
+    mixer = {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 3,
+             "mask": {"size": CONTEXT}, "rot": {"dims": 128, "base": 1e6, "scaling": {"factor": 4.0, "original": 512, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"kind": "moe", "router": {"experts": PIFELIX_EXPERTS, "top": PIFELIX_TOP}, "expert": {"ff": z["ff"], "limit": 7.0}}
+    layers = [{"type": "attention", "mixer": dict(mixer, **({} if t == "own" else {"kv_from": 1})), "mlp": mlp} for t in PIFELIX_LAYERS]
+    return {"architecture": "Pifelix", "vocab": 50272, "width": z["width"], "residual_mult": 0.5, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5}, "init_std": 0.02, "max_positions": CONTEXT, "layers": layers}
+
+
+def build_vononex(size, dtype="bfloat16", config=None):
     import torch
     from transformers_neuronx_b200.config import config_from_dict
     from transformers_neuronx_b200.engine import build_model
     from transformers_neuronx_b200.models.decoder import DecoderModel
-    arch, cfg = config_from_dict(vononex_config(size))
+    arch, cfg = config_from_dict(config(size) if config is not None else vononex_config(size))
     spec = arch.build_spec(cfg)
     dev = torch.device("cuda:0")
     g = torch.Generator(device=dev).manual_seed(0)
@@ -408,6 +429,9 @@ def step_bytes(model, batch, ctx, tables_bytes):
     """Bytes one decode step has to move: every weight once (of the embedding table only the batch's rows), the
     live requests' pages, and every recurrent state read and written."""
     n = model.parameter_bytes() - tables_bytes
+    for part in model.all_parts():                 # routed experts: only those that the batch's tokens are expected to choose
+        if hasattr(part, "step_bytes"):
+            n -= part.parameter_bytes() - part.step_bytes(batch)
     for need in model.cache_needs().values():
         if hasattr(need, "bytes_per_page"):
             n += batch * ctx * need.bytes_per_page(16, model.act_dtype) // 16
@@ -415,7 +439,7 @@ def step_bytes(model, batch, ctx, tables_bytes):
             k = 1
             for d in need.shape:
                 k *= d
-            n += 2 * batch * k * 4
+            n += 2 * batch * k * (2 if getattr(need, "dtype", "") == "activation" else 4)
     return n
 
 
@@ -450,7 +474,13 @@ def profile_families(model, cfg, batch, prompt_tokens):
     return out
 
 
-def workload_vononex(steps, warmup, sizes=None, only=None, batch=8):
+def workload_pifelix(steps, warmup, sizes=None, only=None, batch=8):
+    """workload_vononex for the Pifelix decoder."""
+    return workload_vononex(steps, warmup, sizes, only, batch, design="pifelix", table=PIFELIX_SIZES, layers=PIFELIX_LAYERS,
+                            config=pifelix_config)
+
+
+def workload_vononex(steps, warmup, sizes=None, only=None, batch=8, design="vononex", table=None, layers=None, config=None):
     """Prefill (one 2,048-token prompt) and decode (batch 1, 8, 64, contexts ending at 2,048) of a four-layer
     Vononex decoder, and of a four-layer OPT decoder of the same width and heads, in bfloat16 with random
     weights; per layer, with the decode step's share of the memory roofline and every kernel family's time."""
@@ -458,23 +488,24 @@ def workload_vononex(steps, warmup, sizes=None, only=None, batch=8):
     global DTYPE
     DTYPE = "bfloat16"
     hbm_gbs, tflops, peak_src = peaks()
-    rows = {"peaks": peak_src, "layers": list(VONONEX_LAYERS)}
+    table, layers = table or VONONEX_SIZES, layers or VONONEX_LAYERS
+    rows = {"peaks": peak_src, "layers": list(layers)}
     if only is not None:                       # one part of one size alone (for profiling a small case)
-        model, cfg = build_vononex((sizes or ["2048"])[0])
+        model, cfg = build_vononex((sizes or ["2048"])[0], config=config)
         if only == "decode":
             ms, launches, _, _ = time_decode(model, cfg, batch, steps, warmup)
             return {"only": only, "batch": batch, "ms_per_step": round(ms, 4), "launches": launches}
         return {"only": only, "tokens": PREFILL_TOKENS, "ms": round(time_prefill(model, cfg, steps, warmup), 4)}
-    for size in (sizes or sorted(VONONEX_SIZES)):
-        z = VONONEX_SIZES[size]
+    for size in (sizes or sorted(table)):
+        z = table[size]
         opt_cfg = dict(OPT_6_7B, hidden_size=z["width"], num_attention_heads=z["heads"], ffn_dim=4 * z["width"],
                        word_embed_proj_dim=z["width"])
-        for which in ("vononex", "opt"):
-            if which == "vononex":
-                model, cfg = build_vononex(size)
+        for which in (design, "opt"):
+            if which == design:
+                model, cfg = build_vononex(size, config=config)
                 tables = cfg.vocab * cfg.width * 2                    # the embedding table: rows of the batch only
             else:
-                model, cfg = build(len(VONONEX_LAYERS), dtype="bfloat16", base=opt_cfg)
+                model, cfg = build(len(layers), dtype="bfloat16", base=opt_cfg)
                 tables = (cfg.max_position_embeddings + 2) * cfg.hidden_size * 2      # the output matrix is the token table
             row = {"weights_gb": round(model.parameter_bytes() / 1e9, 3)}
             pf = time_prefill(model, cfg, max(3, min(steps, 5)), 3)
@@ -497,6 +528,8 @@ def extra_workload(name, steps, warmup, sizes=None, only=None, batch=8):
     """One of the further workloads alone, printed as one JSON line of its own."""
     if name == "vononex":
         res = workload_vononex(steps, warmup, sizes, only, batch)
+    elif name == "pifelix":
+        res = workload_pifelix(steps, warmup, sizes, only, batch)
     elif name == "family":
         res = workload_family(steps, warmup, sizes)
     elif name == "sweep":
@@ -532,7 +565,7 @@ def main():
     ap.add_argument("--skip-large", action="store_true", help="leave out the OPT-13B and OPT-30B workloads")
     ap.add_argument("--dtype", default="float16", choices=["float16", "bfloat16"],
                     help="the serving type (float16 is what OPT checkpoints are stored in)")
-    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b", "family", "sweep", "vononex"],
+    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b", "family", "sweep", "vononex", "pifelix"],
                     help="run one of the further workloads instead of the default line")
     ap.add_argument("--sizes", default=None, help="for --workload family: comma-separated sizes (default: all of 125m .. 66b); for --workload vononex: "
                     "widths (2048, 4096)")

@@ -60,6 +60,8 @@ struct Params {
                                  // through distributed shared memory instead of scratch memory
     int sk_tiles;                // paired kernel: the last sk_tiles output tiles are shared out by K blocks
     int sk_pairs;                // ... over the first sk_pairs pairs
+    const int* group_of_tile;    // grouped product (normal form, 128 x 128 tiles): the group of every 128-token tile, -1: none;
+    int group_rows;              //   W holds group_rows rows per group, a tile of group g reads W's rows from g * group_rows on
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -362,6 +364,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_p = blockIdx.x, tile_q = blockIdx.y, split = blockIdx.z;
+    // A grouped product: every tile of tokens belongs to one group (an expert) and multiplies that group's rows of W.
+    // Which group is written by the kernel before this one, so it is read behind the dependency wait; a tile without
+    // a group has nothing to do (nothing has been set up yet, so the whole CTA may leave).
+    int q_row0 = tile_q * BN;
+    if (!SWAP && p.group_of_tile != nullptr) {
+        pdl_wait();
+        const int g = p.group_of_tile[tile_p];
+        if (g < 0) return;
+        q_row0 += g * p.group_rows;
+    }
     // Split K summed in a cluster, swapped form, 2, 4 or 8 splits: every CTA sends the bands of its partial tile
     // to their owners (one bulk copy from shared memory to shared memory each) and adds up what it receives
     // with plain shared-memory loads.  The staging area (a tile) and the receive area (S - 1 bands of it) must
@@ -385,7 +397,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         uint8_t* a_dst = smem + (size_t)s * STAGE_BYTES;
         const int kx = (kb_begin + i) * BLOCK_K;
         if (SWAP) tma_load_2d(a_dst, &map_p, &full_bar[s], kx, tile_p * TILE_P);
-        else tma_load_2d(a_dst + A_BYTES, &map_q, &full_bar[s], kx, tile_q * BN);
+        else tma_load_2d(a_dst + A_BYTES, &map_q, &full_bar[s], kx, q_row0);
     };
     auto load_activations = [&](int i) {
         const int s = i % STAGES;
@@ -1538,6 +1550,25 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
     if (bn == 32) return launch<32, 5, true>(mp, mq, p, grid, stream);
     if (bn == 64) return launch<64, 4, true>(mp, mq, p, grid, stream);
     return launch<128, 3, true>(mp, mq, p, grid, stream);
+}
+
+// A grouped product: C[m, :] = A[m, :] W_g^T for the rows m of every 128-row tile, g = group_of_tile[m / 128] (a device
+// array written by an earlier kernel; -1: the tile is skipped).  W holds the groups' matrices one after the other,
+// [groups * N, K]; A is [M, K] with M a multiple of 128; C is [M, ldc] in the 16-bit type or 32-bit.  No bias, no
+// activation: what follows a group's product is the caller's own kernel.
+TNX_EXPORT int tnx_gemm_tc_grouped(const void* A, const void* W, void* C, int M, int N, int K, int groups, int lda, int ldw,
+                                   int ldc, int c_h16, const int* group_of_tile, int* err_word, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || groups <= 0) return 0;
+    if (M % TILE_P || K <= 0 || K % 8 || lda % 8 || ldw % 8 || lda < K || ldw < K || ldc < N) return TNX_ERR_UNSUPPORTED;
+    if ((((uintptr_t)A | (uintptr_t)W) & 15) || (long long)groups * N >= (1ll << 31)) return TNX_ERR_UNSUPPORTED;
+    if (!err_word || !group_of_tile) return TNX_ERR_BAD_ARG;
+    Params p{};
+    p.K = K; p.ldc = ldc; p.act = TNX_ACT_NONE; p.c_is_h16 = c_h16; p.C = C; p.err = err_word;
+    p.rows_p = M; p.rows_q = N; p.splits = 1; p.kb_per_split = (K + BLOCK_K - 1) / BLOCK_K;
+    p.group_of_tile = group_of_tile; p.group_rows = N;
+    CUtensorMap mp, mq;
+    if (!make_map(&mp, A, M, K, lda, TILE_P) || !make_map(&mq, W, groups * N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
+    return launch<128, 6, false>(mp, mq, p, dim3(M / TILE_P, (N + 127) / 128, 1), stream);
 }
 
 // ---- a wait that runs out, for the tests of the error path --------------------------------------------

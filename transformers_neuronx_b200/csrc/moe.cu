@@ -77,22 +77,19 @@ moe_router_kernel(const T* __restrict__ h, int ld, const TW* __restrict__ wr, co
     }
     __syncthreads();
     if (warp != 0) return;
+    // The choice is made on the logits: both scores grow with them, and a sigmoid that has run out of bits near 1
+    // would tie experts that their logits still tell apart.
+    float mx = -INFINITY, sum = 0.f;
     if (softmax_scores) {
-        float mx = -INFINITY;
         for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
         mx = warp_max(mx);
-        float sum = 0.f;
-        for (int e = lane; e < E; e += 32) { const float v = expf(z[e] - mx); z[e] = v; sum += v; }
+        for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
         sum = warp_sum(sum);
-        for (int e = lane; e < E; e += 32) z[e] /= sum;
-    } else {
-        for (int e = lane; e < E; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
     }
-    __syncwarp();
     float chosen_w[MAX_TOP];
     int chosen[MAX_TOP];
     float total = 0.f;
-    for (int j = 0; j < top; ++j) {                         // the largest score left; of equal ones the lowest index
+    for (int j = 0; j < top; ++j) {                         // the largest logit left; of equal ones the lowest index
         float best = -INFINITY;
         int arg = 0x7fffffff;
         for (int e = lane; e < E; e += 32) {
@@ -105,7 +102,9 @@ moe_router_kernel(const T* __restrict__ h, int ld, const TW* __restrict__ wr, co
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
-        chosen[j] = arg; chosen_w[j] = best; total += best;
+        chosen[j] = arg;
+        chosen_w[j] = softmax_scores ? expf(best - mx) / sum : 1.f / (1.f + expf(-best));
+        total += chosen_w[j];
         if (lane == 0) z[arg] = -INFINITY;
         __syncwarp();
     }

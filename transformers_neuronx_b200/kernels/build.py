@@ -50,6 +50,7 @@ SOURCES: Dict[str, str] = {
     "gated_act": "gated_act.cu",
     "conv_qkv": "conv_qkv.cu",
     "moe": "moe.cu",
+    "moe_grouped": "moe_grouped.cu",
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

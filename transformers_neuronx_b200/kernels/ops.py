@@ -928,7 +928,75 @@ def moe_experts(h, gate_up, down, ids, weights, y, out, gate_max, up_min, up_max
 
 
 def moe_grouped_supported(h, gate_up, down) -> bool:
-    return False
+    """Whether the grouped tensor-core form takes these tensors: a 16-bit engine whose experts are stored in its own
+    16-bit type, widths that are multiples of 8 (16-byte row pitches for the TMA descriptors), at most 1024 experts."""
+    if h.dtype not in _H16 or gate_up.dtype != h.dtype or down.dtype != h.dtype:
+        return False
+    E, F2, W = gate_up.shape
+    return (W % 8 == 0 and (F2 // 2) % 8 == 0 and E <= 1024 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
+            and gate_up.data_ptr() % 16 == 0 and down.data_ptr() % 16 == 0 and E * max(F2, W) < 2 ** 31)
+
+
+def gemm_tc_grouped(a, w, out, group_of_tile):
+    """out[m] = a[m] @ w[g]^T for the rows m of every 128-row tile, g = group_of_tile[m // 128] (-1: the tile is
+    skipped).  a [M, K] (M a multiple of 128) and w [groups, N, K] in one 16-bit type; out [M, N] in that type or 32-bit."""
+    lib = _lib("gemm_tc", a, w, out)
+    _need(a, "a", _H16, 2); _need(w, "w", a.dtype, 3); _need(out, "out", _FLOATS, 2)
+    _need(group_of_tile, "group_of_tile", torch.int32, 1)
+    M, K = a.shape
+    G, N, Kw = w.shape
+    if Kw != K or tuple(out.shape) != (M, N) or M % 128 or group_of_tile.shape[0] < M // 128:
+        raise KernelError(f"grouped product shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    st = _state(a.device)
+    _check(lib.tnx_gemm_tc_grouped(_p(a), _p(w), _p(out), c_int(M), c_int(N), c_int(K), c_int(G), c_int(K), c_int(K), c_int(N),
+                                   c_int(_is_h16(out)), _p(group_of_tile), _p(st["err"]), _stream()), "gemm_tc_grouped")
+
+
+def moe_grouped(ctx, h, gate_up, down, ids, weights, out, gate_max, up_min, up_max, alpha, up_shift, weight_on_input=True,
+                accumulate=False):
+    """moe_experts for many rows: the (row, expert) pairs sorted by expert into 128-row tiles, the experts' two
+    products as grouped tensor-core products, the activation between them and the sum over a row's experts as
+    kernels of csrc/moe_grouped.cu.  Buffers come from ctx.scratch; nothing is read on the host."""
+    lib = _lib("moe_grouped", h, gate_up)
+    if not moe_grouped_supported(h, gate_up, down):
+        raise KernelError("the grouped form takes a 16-bit engine, experts stored in its type and widths that are multiples of 8")
+    N, W = h.shape
+    E, F2, _ = gate_up.shape
+    F, top = F2 // 2, ids.shape[1]
+    P = N * top
+    tiles = lib.tnx_moe_grouped_max_tiles(c_int(P), c_int(E))
+    rows = tiles * 128
+    group_of_tile = ctx.scratch(1, tiles, torch.int32).view(-1)
+    row_of_pair = ctx.scratch(1, P, torch.int32).view(-1)
+    x = ctx.scratch(rows, W, h.dtype)
+    moe_sort_rows(lib, h, ids, weights, E, tiles, group_of_tile, row_of_pair, x, weight_on_input)
+    gu = ctx.scratch(rows, F2, h.dtype)
+    gemm_tc_grouped(x, gate_up, gu, group_of_tile)
+    y = ctx.scratch(rows, F, h.dtype)
+    moe_activation(lib, gu, y, group_of_tile, gate_max, up_min, up_max, alpha, up_shift)
+    per_pair = ctx.scratch(rows, W, torch.float32)
+    gemm_tc_grouped(y, down, per_pair, group_of_tile)
+    moe_combine(lib, per_pair, row_of_pair, weights, out, accumulate, weight_on_input)
+
+
+def moe_sort_rows(lib, h, ids, weights, n_experts, tiles, group_of_tile, row_of_pair, x, weight_on_input):
+    """The plan (every pair's row, every tile's expert) and the rows themselves, x[row(pair)] = weight * h[token]."""
+    P, top = ids.numel(), ids.shape[1]
+    _check(lib.tnx_moe_plan(_p(ids), c_int(P), c_int(n_experts), c_int(tiles), _p(group_of_tile), _p(row_of_pair), _stream()),
+           "moe_plan")
+    _check(lib.tnx_moe_gather(_p(h), c_int(h.stride(0)), _p(weights), _p(row_of_pair), _p(x), c_int(P), c_int(h.shape[1]),
+                              c_int(top), c_int(1 if weight_on_input else 0), _stream()), "moe_gather")
+
+
+def moe_activation(lib, gu, y, group_of_tile, gate_max, up_min, up_max, alpha, up_shift):
+    _check(lib.tnx_moe_act(_p(gu), _p(y), _p(group_of_tile), c_int(gu.shape[0]), c_int(y.shape[1]), c_float(gate_max),
+                           c_float(up_min), c_float(up_max), c_float(alpha), c_float(up_shift), _stream()), "moe_act")
+
+
+def moe_combine(lib, per_pair, row_of_pair, weights, out, accumulate, weight_on_input):
+    N, W = out.shape
+    _check(lib.tnx_moe_combine(_p(per_pair), _p(row_of_pair), _p(weights), _p(out), c_int(N), c_int(W), c_int(weights.shape[1]),
+                               c_int(1 if accumulate else 0), c_int(1 if weight_on_input else 0), _stream()), "moe_combine")
 
 
 def rotary_qkv_prep(proj, q_off, k_off, v_off, token_request, positions, q_weight, k_weight, eps, head_scale,

@@ -109,7 +109,7 @@ class OutputNormBlock(ScaledPostNormBlock):
     def __init__(self, norm1, mixer, norm2, feed_forward, layer_spec=None):
         self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
         self.residual_scale = float(getattr(layer_spec, "residual_scale", 1.0))
-        for n in (norm1, norm2 if feed_forward is not None else None):
+        for n in (norm1,) + ((norm2,) if feed_forward is not None else ()):
             if n is None or not hasattr(n, "forward_add"):
                 raise ValueError(f"an output_norm block needs norms that add a normalised sublayer output to the stream; "
                                  f"{type(n).__name__} does not")

@@ -27,7 +27,7 @@ from .spec import RoutedFeedForwardSpec
 class RoutedExperts(FeedForward):
     graph_safe = True
     can_overwrite = True
-    libraries = ("moe",)
+    libraries = ("moe", "moe_grouped", "gemm_tc")
     GROUPED_FROM = 64        # rows from which the grouped tensor-core form runs (16-bit engines)
 
     def __init__(self, spec: RoutedFeedForwardSpec):
@@ -65,11 +65,12 @@ class RoutedExperts(FeedForward):
         return sum(t.numel() * t.element_size() for t in (self.router, self.gate_up, self.down))
 
     def step_bytes(self, n_tokens: int) -> int:
-        """Bytes of weights a step of n_tokens reads at most (every expert once it is chosen by somebody)."""
+        """Bytes of weights a step of n_tokens is expected to read: every expert once that some token chooses, with
+        tokens that choose independently and evenly."""
         s = self.spec
-        used = min(s.n_experts, n_tokens * s.top)
+        used = s.n_experts * (1.0 - (1.0 - s.top / s.n_experts) ** n_tokens)
         per = (self.gate_up[0].numel() + self.down[0].numel()) * self.gate_up.element_size()
-        return self.router.numel() * self.router.element_size() + used * per
+        return int(self.router.numel() * self.router.element_size() + used * per)
 
     def forward(self, ctx, h, out, accumulate=True):
         s, N = self.spec, h.shape[0]
