@@ -77,8 +77,11 @@ def _step_arrays(cuts):
     (2, 2, 128, 96, 8, 64, False, None, torch.float32),                   # pairs (i, i + dims/2) as other designs want them
     (5, 1, 48, 48, 1, 48, True, None, torch.float32),                     # one tap: a scale per channel, nothing kept
     (4, 2, 64, 48, 3, 64, True, (4.0, 512, 32.0, 1.0), torch.bfloat16),
+    (3, 1, 96, 32, 4, 40, True, None, torch.bfloat16),                    # 12 lanes a head, two heads a warp, a padded value head
+    (2, 2, 256, 8, 2, 256, True, None, torch.float32),
 ])
-def test_convolution_norm_and_rotation_across_cuts(H, G, dk, dv, taps, rdims, inter, scaling, dtype):
+@pytest.mark.parametrize("col0", [5, 8])                                  # 8: the addresses allow the kernel of 8-channel pieces
+def test_convolution_norm_and_rotation_across_cuts(H, G, dk, dv, taps, rdims, inter, scaling, dtype, col0):
     """Two requests cut into unequal steps side by side (single tokens, pairs, a padded row, a request left out of a
     step): what a token reads from the state equals what it would have read from the rows of a longer step."""
     from transformers_neuronx_b200.kernels import ops
@@ -118,12 +121,12 @@ def test_convolution_norm_and_rotation_across_cuts(H, G, dk, dv, taps, rdims, in
         req, pos, q_start, q_len, slots = _step_arrays(cuts)
         rows = torch.cat([u[r, at[r]:at[r] + n] for r, n in zip(reqs, [c[2] for c in cuts])])
         N = rows.shape[0]
-        proj = torch.zeros(N + 1, 5 + C, dtype=dtype)
-        proj[:N, 5:] = rows
+        proj = torch.zeros(N + 1, (col0 + C + 3) if col0 % 8 else -(-(col0 + C + 3) // 8) * 8, dtype=dtype)
+        proj[:N, col0:col0 + C] = rows
         ctx = SimpleNamespace(token_request=_i32(req + [-1]), positions=_i32(pos + [0]), q_start=_i32(q_start + [0]),
                               q_len=_i32(q_len + [0]), state_slots=_i32(slots + [-1]), decode_only=all(n == 1 for n in q_len))
         qo, ko, vo = (torch.full((N + 1, n * D), 9.0, device=DEV, dtype=dtype) for n in (H, max(G, 1), max(G, 1)))
-        ops.conv_qkv_prep(proj.to(DEV), 5, w.to(DEV), taps, state, ctx, gq.to(DEV), gk.to(DEV) if G else None, 1e-4, freq,
+        ops.conv_qkv_prep(proj.to(DEV), col0, w.t().contiguous().to(DEV), taps, state, ctx, gq.to(DEV), gk.to(DEV) if G else None, 1e-4, freq,
                           rdims, inter, rotation_magnitude(fs), qo, ko if G else None, vo if G else None, H, G, dk, dv, D)
         assert float((qo[N].float() - 9.0).abs().max()) == 0.0   # the padded row is left alone
         row = 0

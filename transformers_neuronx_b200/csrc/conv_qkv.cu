@@ -16,8 +16,11 @@
 // state in the same kernel (no other row reads it); requests with several rows are brought up to date by
 // conv_state_update_kernel, launched after every row has read the old state.
 //
-// One thread block per token, one warp per head (of queries, keys or values) at a time; a lane owns the pairs
-// (2 lane, 2 lane + 1) + 64 r of the head, so that an interleaved rotation stays inside the lane.
+// Two kernels do this.  conv_norm_rotate_vec_kernel takes head sizes that are multiples of 8 with interleaved pairs (or no
+// rotation) and up to four taps: a lane owns 8 consecutive channels of a head (16-byte loads and stores in a 16-bit type,
+// four pairs of a rotation inside the lane), the dims/8 lanes of a head sit side by side in a warp, several heads a warp.
+// conv_norm_rotate_kernel takes everything else: one thread block per token, one warp per head at a time, a lane owns
+// the pairs (2 lane, 2 lane + 1) + 64 r of the head.
 #include "common.cuh"
 
 namespace {
@@ -27,7 +30,7 @@ constexpr int MAX_TAPS = 8;
 template <typename T>
 struct ConvPrep {
     const T* proj; int ld; int col0;             // the mixer's projections begin at column col0: queries, keys, values
-    const float* conv_w; int taps;              // [channels, taps] or null (no convolution; taps is 1 then)
+    const float* conv_w; int taps;              // [taps, channels] or null (no convolution; taps is 1 then)
     T* state;                                   // [slots, taps - 1, channels]
     const int* token_request; const int* positions; const int* q_start; const int* q_len; const int* state_slots;
     const float* q_norm; const float* k_norm; float eps;      // [dk] each, or null
@@ -69,7 +72,6 @@ __global__ void __launch_bounds__(128) conv_norm_rotate_kernel(const ConvPrep<T>
                     if (p.conv_w == nullptr) {
                         y = cur;
                     } else {
-                        const float* w = p.conv_w + (size_t)ch * taps;
                         float past[MAX_TAPS];                   // past[b]: the projected value b positions back
                         past[0] = cur;
                         for (int b = 1; b < taps; ++b) {
@@ -80,7 +82,7 @@ __global__ void __launch_bounds__(128) conv_norm_rotate_kernel(const ConvPrep<T>
                             }
                             past[b] = v;
                         }
-                        for (int j = 0; j < taps; ++j) y = fmaf(w[j], past[taps - 1 - j], y);
+                        for (int j = 0; j < taps; ++j) y = fmaf(p.conv_w[(size_t)j * p.channels + ch], past[taps - 1 - j], y);
                         if (alone && st) {                      // oldest first: what was one back is now two back
                             for (int s = 0; s < keep; ++s)
                                 st[(size_t)s * p.channels + ch] = from_float<T>(past[keep - 1 - s]);
@@ -158,6 +160,130 @@ __global__ void __launch_bounds__(128) conv_norm_rotate_kernel(const ConvPrep<T>
     }
 }
 
+template <typename T> struct Vec8;
+template <> struct Vec8<h16> {
+    uint4 raw;
+    __device__ __forceinline__ void load(const h16* p) { raw = *(const uint4*)p; }
+    __device__ __forceinline__ void store(h16* p) const { *(uint4*)p = raw; }
+    __device__ __forceinline__ void zero() { raw = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ void get(float (&v)[8]) const {
+        const h16x2* h = (const h16x2*)&raw;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = h16x2_to_float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+    __device__ __forceinline__ void set(const float (&v)[8]) {
+        h16x2* h = (h16x2*)&raw;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = floats_to_h16x2(v[2 * i], v[2 * i + 1]);
+    }
+};
+template <> struct Vec8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) { a = *(const float4*)p; b = *(const float4*)(p + 4); }
+    __device__ __forceinline__ void store(float* p) const { *(float4*)p = a; *(float4*)(p + 4) = b; }
+    __device__ __forceinline__ void zero() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
+    __device__ __forceinline__ void get(float (&v)[8]) const {
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    __device__ __forceinline__ void set(const float (&v)[8]) {
+        a = make_float4(v[0], v[1], v[2], v[3]); b = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+
+// TAPS: the convolution's taps, 1 when there is none.  grid (tokens, groups of four warps); a warp takes 32 / (dims / 8)
+// heads: first those of queries and keys (which lie side by side in the projection and have one size), then the values'.
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(128) conv_norm_rotate_vec_kernel(const ConvPrep<T> p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n = blockIdx.x, lane = threadIdx.x & 31;
+    const int req = p.token_request[n];
+    if (req < 0) return;                                    // a padded row of a captured step
+    const int Lk = p.dk >> 3, Lv = p.dv >> 3;
+    const int per_k = 32 / Lk, per_v = Lv ? 32 / Lv : 1, n_qk = p.H + p.G;
+    const int warps_qk = (n_qk + per_k - 1) / per_k, warps_v = p.G ? (p.G + per_v - 1) / per_v : 0;
+    const int w = blockIdx.y * 4 + (threadIdx.x >> 5);
+    if (w >= warps_qk + warps_v) return;
+    const bool values = w >= warps_qk;
+    const int L = values ? Lv : Lk, dims = values ? p.dv : p.dk;
+    const int unit = (values ? (w - warps_qk) * per_v : w * per_k) + lane / L, piece = lane % L;
+    const bool active = lane < (32 / L) * L && unit < (values ? p.G : n_qk);
+    const int ch = (values ? n_qk * p.dk + unit * p.dv : unit * p.dk) + piece * 8;
+    const int pos = p.positions[n], idx = n - p.q_start[req], slot = p.state_slots[req];
+    constexpr int KEEP = TAPS - 1;
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = 0.f;
+    if (active) {
+        const T* row = p.proj + (size_t)n * p.ld + p.col0 + ch;
+        T* st = (KEEP > 0 && slot >= 0) ? p.state + (size_t)slot * KEEP * p.channels + ch : nullptr;
+        Vec8<T> past[TAPS];                                 // past[b]: the projected values b positions back
+        past[0].load(row);
+#pragma unroll
+        for (int b = 1; b < TAPS; ++b) {
+            past[b].zero();
+            if (pos - b >= 0) {
+                if (idx - b >= 0) past[b].load(row - (ptrdiff_t)b * p.ld);
+                else if (st) past[b].load(st + (size_t)(KEEP + idx - b) * p.channels);
+            }
+        }
+        if (p.conv_w == nullptr) {
+            past[0].get(y);
+        } else {
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) {
+                float u[8];
+                past[TAPS - 1 - j].get(u);
+                const float4 w0 = *(const float4*)(p.conv_w + (size_t)j * p.channels + ch);
+                const float4 w1 = *(const float4*)(p.conv_w + (size_t)j * p.channels + ch + 4);
+                y[0] = fmaf(w0.x, u[0], y[0]); y[1] = fmaf(w0.y, u[1], y[1]); y[2] = fmaf(w0.z, u[2], y[2]); y[3] = fmaf(w0.w, u[3], y[3]);
+                y[4] = fmaf(w1.x, u[4], y[4]); y[5] = fmaf(w1.y, u[5], y[5]); y[6] = fmaf(w1.z, u[6], y[6]); y[7] = fmaf(w1.w, u[7], y[7]);
+            }
+            if (st && p.q_len[req] == 1) {                  // oldest first: what was one back is now two back
+#pragma unroll
+                for (int s = 0; s < KEEP; ++s) past[KEEP - 1 - s].store(st + (size_t)s * p.channels);
+            }
+        }
+    }
+    const bool is_q = !values && unit < p.H;
+    const float* g = values ? nullptr : (is_q ? p.q_norm : p.k_norm);
+    if (!values) {
+        float ssq = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ssq = fmaf(y[i], y[i], ssq);
+        const int seg = (lane / L) * L;
+        float total = 0.f;
+        for (int o = 0; o < L; ++o) total += __shfl_sync(0xffffffffu, ssq, (seg + o) & 31);
+        if (active && g != nullptr) {
+            const float rinv = 1.0f / sqrtf(total / (float)dims + p.eps);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] *= rinv * g[piece * 8 + i];
+        }
+        if (active && p.rot_dims > 0) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int c = piece * 8 + 2 * t;
+                if (c + 1 < p.rot_dims) {
+                    float sn, cs;
+                    sincosf((float)pos * p.inv_freq[c >> 1], &sn, &cs);
+                    sn *= p.magnitude; cs *= p.magnitude;
+                    const float a = y[2 * t], b = y[2 * t + 1];
+                    y[2 * t] = a * cs - b * sn;
+                    y[2 * t + 1] = b * cs + a * sn;
+                }
+            }
+        }
+    }
+    if (!active) return;
+    T* out = values ? p.v_out + ((size_t)n * p.G + unit) * p.D
+                    : (is_q ? p.q_out + ((size_t)n * p.H + unit) * p.D : p.k_out + ((size_t)n * p.G + (unit - p.H)) * p.D);
+    Vec8<T> o;
+    o.set(y);
+    o.store(out + piece * 8);
+    o.zero();
+    for (int pp = L + piece; pp < (p.D >> 3); pp += L) o.store(out + pp * 8);       // the head's padding
+}
+
 // After a step: the state of every request with more than one row (q_len 1: the kernel above did it) becomes its last
 // taps - 1 projected values.  A thread owns a channel and walks the state from the oldest entry on: what it reads
 // (further on in the old state, or this step's rows) it has not yet overwritten.
@@ -193,7 +319,25 @@ int launch(const void* proj, int ld, int col0, const float* conv_w, int taps, vo
     p.rot_dims = inv_freq ? rot_dims : 0; p.interleaved = interleaved; p.magnitude = magnitude;
     p.q_out = (T*)q_out; p.k_out = (T*)k_out; p.v_out = (T*)v_out; p.H = H; p.G = G; p.dk = dk; p.dv = dv; p.D = D;
     p.channels = H * dk + G * (dk + dv);
-    int rc = tnx_launch_in_order(conv_norm_rotate_kernel<T>, dim3(N), dim3(128), 0, stream, p);
+    // the vectorised kernel where the sizes and addresses allow 8-channel pieces
+    const size_t el = sizeof(T);
+    const bool vec = dk % 8 == 0 && (G == 0 || dv % 8 == 0) && D % 8 == 0 && (p.rot_dims == 0 || interleaved) && p.taps <= 4 &&
+                     ld % 8 == 0 && col0 % 8 == 0 && ((uintptr_t)proj * 1) % 16 == 0 && ((uintptr_t)state % 16) == 0 &&
+                     ((uintptr_t)conv_w % 16) == 0 && (((uintptr_t)q_out | (uintptr_t)k_out | (uintptr_t)v_out) % 16) == 0 && el >= 2;
+    int rc;
+    if (vec) {
+        const int per_k = 32 / (dk / 8), per_v = G ? 32 / (dv / 8) : 1;
+        const int warps = (H + G + per_k - 1) / per_k + (G ? (G + per_v - 1) / per_v : 0);
+        const dim3 grid(N, (warps + 3) / 4);
+        switch (p.taps) {
+            case 1: rc = tnx_launch_in_order(conv_norm_rotate_vec_kernel<T, 1>, grid, dim3(128), 0, stream, p); break;
+            case 2: rc = tnx_launch_in_order(conv_norm_rotate_vec_kernel<T, 2>, grid, dim3(128), 0, stream, p); break;
+            case 3: rc = tnx_launch_in_order(conv_norm_rotate_vec_kernel<T, 3>, grid, dim3(128), 0, stream, p); break;
+            default: rc = tnx_launch_in_order(conv_norm_rotate_vec_kernel<T, 4>, grid, dim3(128), 0, stream, p); break;
+        }
+    } else {
+        rc = tnx_launch_in_order(conv_norm_rotate_kernel<T>, dim3(N), dim3(128), 0, stream, p);
+    }
     if (rc != 0 || !update_state || p.taps <= 1 || n_requests <= 0) return rc;
     return tnx_launch_in_order(conv_state_update_kernel<T>, dim3((p.channels + 127) / 128, n_requests), dim3(128), 0, stream,
                                (const T*)proj, ld, col0, (T*)state, p.taps - 1, p.channels, q_start, q_len, state_slots);

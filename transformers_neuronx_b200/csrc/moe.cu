@@ -9,12 +9,13 @@
 //
 // Kernels of this file (T: the activations' type, TW: the stored type of the experts' matrices):
 //   moe_router_kernel      a block a token: logits, scores, the top experts and their weights
-//   moe_gate_up_kernel     a block per (token, chosen expert, slice of the inner width): the token's row in shared
-//                          memory, a warp per inner feature, 16-byte loads along the matrices' rows
-//   moe_down_kernel        a block per (token, slice of the width): sums the chosen experts' down products in the order of
-//                          the choice and writes or adds the 32-bit result
-// They stream each chosen expert's matrices once per token: the form for steps of few tokens.  Steps of many tokens
-// take the grouped tensor-core products of moe_grouped.cu.
+//   moe_gate_up_kernel     a block per (expert, slice of the inner width): the inputs of the tokens that chose the expert
+//                          in shared memory (four at a time), a warp per inner feature, 16-byte loads along the rows
+//   moe_down_kernel        a block per (expert, slice of the width): the same for the down product, one 32-bit row per pair
+//   moe_sum_kernel         adds a token's pairs up in the order of the choice and writes or adds the 32-bit result
+// They stream a chosen expert's matrices once for every four tokens that chose it, through the multiply-add units: the
+// form for steps of few tokens (and of the 32-bit engine).  Steps of many tokens take the grouped tensor-core products of
+// moe_grouped.cu.
 #include "common.cuh"
 
 namespace {
@@ -127,61 +128,241 @@ __device__ __forceinline__ float expert_act(float g, float u, const ExpertMath& 
     return g / (1.f + expf(-m.alpha * g)) * (u + m.up_shift);
 }
 
+// The pairs (token, choice) that chose expert e, in ascending order, gathered by warp 0 into `list`; returns their number
+// to every thread.  (A step of few tokens: a few hundred pairs at most.)
+__device__ __forceinline__ int pairs_of_expert(const int* __restrict__ ids, int n_pairs, int e, int* list, int* count_s) {
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int count = 0;
+        for (int base = 0; base < n_pairs; base += 32) {
+            const int i = base + lane;
+            const bool mine = i < n_pairs && ids[i] == e;
+            const unsigned mask = __ballot_sync(0xffffffffu, mine);
+            if (mine) list[count + __popc(mask & ((1u << lane) - 1u))] = i;
+            count += __popc(mask);
+        }
+        if (lane == 0) *count_s = count;
+    }
+    __syncthreads();
+    return *count_s;
+}
+
+template <typename T> struct Load8;
+template <> struct Load8<h16> {
+    static __device__ __forceinline__ void get(const h16* p, float (&v)[8]) {
+        const uint4 raw = *(const uint4*)p;
+        const h16x2* h = (const h16x2*)&raw;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = h16x2_to_float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+};
+template <> struct Load8<float> {
+    static __device__ __forceinline__ void get(const float* p, float (&v)[8]) {
+        const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+};
+
+constexpr int MT = 4;          // rows of one expert that share one pass over its matrices
+
+// 8 elements of a matrix as they are loaded (converted when they are used, so that several loads can be in flight).
+template <typename TW> struct Raw8;
+template <> struct Raw8<h16> {
+    uint4 raw;
+    __device__ __forceinline__ void load(const h16* p) { raw = *(const uint4*)p; }
+    __device__ __forceinline__ void get(float (&v)[8]) const {
+        const h16x2* h = (const h16x2*)&raw;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = h16x2_to_float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+    static constexpr int AHEAD = 4;
+};
+template <> struct Raw8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) { a = *(const float4*)p; b = *(const float4*)(p + 4); }
+    __device__ __forceinline__ void get(float (&v)[8]) const {
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static constexpr int AHEAD = 2;
+};
+
+// One pass over the rows `w0` and (when given) `w1` of length K for up to MT staged rows xs[r][K]: acc0[r] = <w0, xs[r]>.
+// A lane asks for AHEAD pieces of 16 bytes of every row before it uses the first: with a row or two of tokens the
+// kernel does little arithmetic per byte, and the bytes in flight are what the memory's rate depends on.
+// R: how many rows are staged, as a constant (a count that is only known when the kernel runs made the compiler issue
+// all rows' instructions under predicates: with eight rows 190 instructions per 16 bytes of weights where two rows need 50).
+template <typename T, typename TW, bool TWO, int R>
+__device__ __forceinline__ void rows_dot_n(const TW* __restrict__ w0, const TW* __restrict__ w1, const T* xs, int K,
+                                           int lane, bool vec, float (&acc0)[MT], float (&acc1)[MT]) {
+    constexpr int U = Raw8<TW>::AHEAD;
+    constexpr int rows = R;
+#pragma unroll
+    for (int r = 0; r < MT; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
+    if (vec) {
+        for (int c = lane * 8; c < K; c += 256 * U) {
+            Raw8<TW> a[U], b[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int cc = c + 256 * u;
+                if (cc < K) { a[u].load(w0 + cc); if (TWO) b[u].load(w1 + cc); }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int cc = c + 256 * u;
+                if (cc < K) {
+                    float af[8], bf[8], x[8];
+                    a[u].get(af);
+                    if (TWO) b[u].get(bf);
+#pragma unroll
+                    for (int r = 0; r < MT; ++r) {
+                        if (r < rows) {
+                            Load8<T>::get(xs + (size_t)r * K + cc, x);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                acc0[r] = fmaf(af[i], x[i], acc0[r]);
+                                if (TWO) acc1[r] = fmaf(bf[i], x[i], acc1[r]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        for (int c = lane; c < K; c += 32) {
+            const float a = to_float(w0[c]), b = TWO ? to_float(w1[c]) : 0.f;
+#pragma unroll
+            for (int r = 0; r < MT; ++r) {
+                if (r < rows) {
+                    const float x = to_float(xs[(size_t)r * K + c]);
+                    acc0[r] = fmaf(a, x, acc0[r]);
+                    if (TWO) acc1[r] = fmaf(b, x, acc1[r]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < MT; ++r) {
+        if (r < rows) {
+            acc0[r] = warp_sum(acc0[r]);
+            if (TWO) acc1[r] = warp_sum(acc1[r]);
+        }
+    }
+}
+template <typename T, typename TW, bool TWO>
+__device__ __forceinline__ void rows_dot(const TW* __restrict__ w0, const TW* __restrict__ w1, const T* xs, int K, int rows,
+                                         int lane, bool vec, float (&acc0)[MT], float (&acc1)[MT]) {
+    switch (rows) {
+        case 1: rows_dot_n<T, TW, TWO, 1>(w0, w1, xs, K, lane, vec, acc0, acc1); break;
+        case 2: rows_dot_n<T, TW, TWO, 2>(w0, w1, xs, K, lane, vec, acc0, acc1); break;
+        case 3: rows_dot_n<T, TW, TWO, 3>(w0, w1, xs, K, lane, vec, acc0, acc1); break;
+        default: rows_dot_n<T, TW, TWO, MT>(w0, w1, xs, K, lane, vec, acc0, acc1); break;
+    }
+}
+
 // gate_up: [E, 2F, W] (an expert's gate rows, then its up rows); y: [N * top, F] in the activations' type.
+// A block per (expert, slice of the inner width): the expert's rows are streamed once for all the tokens that chose it
+// (MT of them at a time, their inputs staged in shared memory in the activations' type); an expert nobody chose costs
+// one look at the choices.
 template <typename T, typename TW>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 moe_gate_up_kernel(const T* __restrict__ h, int ld, const TW* __restrict__ gate_up, const int* __restrict__ ids,
-                   const float* __restrict__ weights, T* __restrict__ y, int W, int F, int top, int per_block, ExpertMath m) {
-    extern __shared__ __align__(16) float x[];             // [W]
+                   const float* __restrict__ weights, T* __restrict__ y, int W, int F, int top, int n_pairs, int per_block,
+                   ExpertMath m) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T* xs = (T*)smem_raw;                                  // [MT][W]
+    int* list = (int*)(smem_raw + (((size_t)MT * W * sizeof(T) + 15) & ~(size_t)15));
+    __shared__ int count_s;
     pdl_launch_dependents();
     pdl_wait();
-    const int pair = blockIdx.x, n = pair / top, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = ids[pair];
-    if (e < 0) return;
-    const float wt = m.weight_on_input ? weights[pair] : 1.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) x[c] = wt * to_float(h[(size_t)n * ld + c]);
-    __syncthreads();
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int count = pairs_of_expert(ids, n_pairs, e, list, &count_s);
+    if (count == 0) return;
     const TW* wg = gate_up + (size_t)e * 2 * F * W;
     const TW* wu = wg + (size_t)F * W;
     const bool vec = W % 8 == 0 && ((uintptr_t)gate_up % 16) == 0;
     const int f_end = min(F, (blockIdx.y + 1) * per_block);
-    for (int f = blockIdx.y * per_block + warp; f < f_end; f += 4) {
-        const float g = warp_dot<TW>(wg + (size_t)f * W, x, W, lane, vec);
-        const float u = warp_dot<TW>(wu + (size_t)f * W, x, W, lane, vec);
-        if (lane == 0) y[(size_t)pair * F + f] = from_float<T>(expert_act(g, u, m));
+    for (int c0 = 0; c0 < count; c0 += MT) {
+        const int rows = min(MT, count - c0);
+        __syncthreads();
+        for (int r = 0; r < rows; ++r) {
+            const int pair = list[c0 + r];
+            const float wt = m.weight_on_input ? weights[pair] : 1.f;
+            const T* src = h + (size_t)(pair / top) * ld;
+            T* dst = xs + (size_t)r * W;
+            if (vec && ld % 8 == 0 && ((uintptr_t)h % 16) == 0) {
+                for (int c = threadIdx.x * 8; c < W; c += blockDim.x * 8) {
+                    float v[8];
+                    Load8<T>::get(src + c, v);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) dst[c + i] = from_float<T>(wt * v[i]);
+                }
+            } else {
+                for (int c = threadIdx.x; c < W; c += blockDim.x) dst[c] = from_float<T>(wt * to_float(src[c]));
+            }
+        }
+        __syncthreads();
+        for (int f = blockIdx.y * per_block + warp; f < f_end; f += 4) {
+            float g[MT], u[MT];
+            rows_dot<T, TW, true>(wg + (size_t)f * W, wu + (size_t)f * W, xs, W, rows, lane, vec, g, u);
+#pragma unroll
+            for (int r = 0; r < MT; ++r)
+                if (r < rows && lane == r) y[(size_t)list[c0 + r] * F + f] = from_float<T>(expert_act(g[r], u[r], m));
+        }
     }
 }
 
-// down: [E, W, F]; out: 32-bit [N, W], written (accumulate 0) or added to.
+// down: [E, W, F]; per_pair: 32-bit [N * top, W], the chosen expert's result for every pair (moe_sum_kernel adds a
+// token's pairs up).  A block per (expert, slice of the width), as above.
 template <typename T, typename TW>
-__global__ void __launch_bounds__(128)
-moe_down_kernel(const T* __restrict__ y, const TW* __restrict__ down, const int* __restrict__ ids,
-                const float* __restrict__ weights, float* out, int W, int F, int top, int per_block, int accumulate,
-                int weight_on_input) {
-    extern __shared__ __align__(16) float ys[];            // [top][F]
+__global__ void __launch_bounds__(128, 4)
+moe_down_kernel(const T* __restrict__ y, const TW* __restrict__ down, const int* __restrict__ ids, float* __restrict__ per_pair,
+                int W, int F, int n_pairs, int per_block) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T* ys = (T*)smem_raw;                                  // [MT][F]
+    int* list = (int*)(smem_raw + (((size_t)MT * F * sizeof(T) + 15) & ~(size_t)15));
+    __shared__ int count_s;
     pdl_launch_dependents();
     pdl_wait();
-    const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (ids[(size_t)n * top] < 0) return;
-    const int Fp = (F + 3) & ~3;
-    for (int i = threadIdx.x; i < top * F; i += blockDim.x) {
-        const int j = i / F, f = i % F;
-        const float wt = weight_on_input ? 1.f : weights[(size_t)n * top + j];
-        ys[j * Fp + f] = wt * to_float(y[((size_t)n * top + j) * F + f]);
-    }
-    __syncthreads();
-    const bool vec = F % 8 == 0 && ((uintptr_t)down % 16) == 0;
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int count = pairs_of_expert(ids, n_pairs, e, list, &count_s);
+    if (count == 0) return;
+    const bool vec = F % 8 == 0 && ((uintptr_t)down % 16) == 0 && ((uintptr_t)y % 16) == 0;
     const int o_end = min(W, (blockIdx.y + 1) * per_block);
-    for (int o = blockIdx.y * per_block + warp; o < o_end; o += 4) {
+    for (int c0 = 0; c0 < count; c0 += MT) {
+        const int rows = min(MT, count - c0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < rows * F; i += blockDim.x) {
+            const int r = i / F, c = i - r * F;
+            ys[(size_t)r * F + c] = y[(size_t)list[c0 + r] * F + c];
+        }
+        __syncthreads();
+        for (int o = blockIdx.y * per_block + warp; o < o_end; o += 4) {
+            float s[MT], unused[MT];
+            rows_dot<T, TW, false>(down + ((size_t)e * W + o) * F, nullptr, ys, F, rows, lane, vec, s, unused);
+#pragma unroll
+            for (int r = 0; r < MT; ++r)
+                if (r < rows && lane == r) per_pair[(size_t)list[c0 + r] * W + o] = s[r];
+        }
+    }
+}
+
+// out[n] (+)= sum over the token's choices, in their order, of per_pair (times the choice's weight where it multiplies
+// the expert's output).
+__global__ void __launch_bounds__(128)
+moe_sum_kernel(const float* __restrict__ per_pair, const int* __restrict__ ids, const float* __restrict__ weights, float* out,
+               int W, int top, int accumulate, int weight_on_input) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n = blockIdx.x;
+    if (ids[(size_t)n * top] < 0) return;                   // a padded row of a captured step
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float s = 0.f;
         for (int j = 0; j < top; ++j) {
-            const int e = ids[(size_t)n * top + j];
-            s += warp_dot<TW>(down + ((size_t)e * W + o) * F, ys + j * Fp, F, lane, vec);
+            const float v = per_pair[((size_t)n * top + j) * W + c];
+            s += weight_on_input ? v : v * weights[(size_t)n * top + j];
         }
-        if (lane == 0) {
-            float* dst = out + (size_t)n * W + o;
-            *dst = accumulate ? *dst + s : s;
-        }
+        float* dst = out + (size_t)n * W + c;
+        *dst = accumulate ? *dst + s : s;
     }
 }
 }  // namespace
@@ -207,28 +388,34 @@ TNX_EXPORT int tnx_moe_route(const void* h, int ld, const void* router, const in
 }
 
 TNX_EXPORT int tnx_moe_experts(const void* h, int ld, const void* gate_up, const void* down, const int* ids,
-                               const float* weights, void* y, float* out, int N, int W, int F, int top, float gate_max,
-                               float up_min, float up_max, float alpha, float up_shift, int weight_on_input, int accumulate,
-                               int h_h16, int w_h16, cudaStream_t stream) {
+                               const float* weights, void* y, float* per_pair, float* out, int N, int W, int F, int top,
+                               int n_experts, float gate_max, float up_min, float up_max, float alpha, float up_shift,
+                               int weight_on_input, int accumulate, int h_h16, int w_h16, cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (W <= 0 || F <= 0 || top <= 0 || top > MAX_TOP) return TNX_ERR_UNSUPPORTED;
-    const size_t smem1 = (size_t)W * sizeof(float), smem2 = (size_t)top * ((F + 3) & ~3) * sizeof(float);
-    if (smem1 > 160 * 1024 || smem2 > 160 * 1024) return TNX_ERR_UNSUPPORTED;
-    ExpertMath m{gate_max, up_min, up_max, alpha, up_shift, weight_on_input};
-    // enough blocks to fill the GPU when the tokens are few, whole rows of work per warp when they are many
+    if (W <= 0 || F <= 0 || top <= 0 || top > MAX_TOP || n_experts <= 0) return TNX_ERR_UNSUPPORTED;
     const int pairs = N * top;
-    int per1 = 4; while (per1 < F && (long long)pairs * ((F + per1 - 1) / per1) > 2048) per1 *= 2;
-    int per2 = 4; while (per2 < W && (long long)N * ((W + per2 - 1) / per2) > 2048) per2 *= 2;
-    const dim3 g1(pairs, (F + per1 - 1) / per1), g2(N, (W + per2 - 1) / per2);
+    const size_t el = h_h16 ? 2 : 4;
+    const size_t smem1 = (((size_t)MT * W * el + 15) & ~(size_t)15) + (size_t)pairs * sizeof(int);
+    const size_t smem2 = (((size_t)MT * F * el + 15) & ~(size_t)15) + (size_t)pairs * sizeof(int);
+    if (smem1 > 200 * 1024 || smem2 > 200 * 1024) return TNX_ERR_UNSUPPORTED;
+    ExpertMath m{gate_max, up_min, up_max, alpha, up_shift, weight_on_input};
+    // slices that give every SM a few blocks of the experts that are chosen
+    const int busy = n_experts < pairs ? n_experts : pairs;
+    int per1 = 4; while (per1 < F && (long long)busy * ((F + per1 - 1) / per1) > 1024) per1 *= 2;
+    int per2 = 4; while (per2 < W && (long long)busy * ((W + per2 - 1) / per2) > 1024) per2 *= 2;
+    const dim3 g1(n_experts, (F + per1 - 1) / per1), g2(n_experts, (W + per2 - 1) / per2);
 #define GO(T, TW)                                                                                                       \
     do {                                                                                                                \
         if (smem1 > 48 * 1024) cudaFuncSetAttribute(moe_gate_up_kernel<T, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1); \
         if (smem2 > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<T, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);    \
         int rc = tnx_launch_in_order(moe_gate_up_kernel<T, TW>, g1, dim3(128), smem1, stream, (const T*)h, ld,          \
-                                     (const TW*)gate_up, ids, weights, (T*)y, W, F, top, per1, m);                      \
+                                     (const TW*)gate_up, ids, weights, (T*)y, W, F, top, pairs, per1, m);               \
         if (rc != 0) return rc;                                                                                         \
-        return tnx_launch_in_order(moe_down_kernel<T, TW>, g2, dim3(128), smem2, stream, (const T*)y, (const TW*)down,  \
-                                   ids, weights, out, W, F, top, per2, accumulate, weight_on_input);                    \
+        rc = tnx_launch_in_order(moe_down_kernel<T, TW>, g2, dim3(128), smem2, stream, (const T*)y, (const TW*)down,    \
+                                 ids, per_pair, W, F, pairs, per2);                                                     \
+        if (rc != 0) return rc;                                                                                         \
+        return tnx_launch_in_order(moe_sum_kernel, dim3(N), dim3(128), 0, stream, (const float*)per_pair, ids, weights, \
+                                   out, W, top, accumulate, weight_on_input);                                           \
     } while (0)
     if (h_h16 && w_h16) GO(h16, h16);
     if (h_h16) GO(h16, float);

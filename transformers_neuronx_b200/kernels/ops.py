@@ -860,8 +860,8 @@ def conv_qkv_prep(proj, col0, conv_w, taps, state, ctx, q_norm, k_norm, eps, inv
     keep = 0
     if conv_w is not None:
         _need(conv_w, "conv_w", torch.float32, 2)
-        if tuple(conv_w.shape) != (channels, taps):
-            raise KernelError(f"conv_w must be [{channels}, {taps}]")
+        if tuple(conv_w.shape) != (taps, channels):
+            raise KernelError(f"conv_w must be [{taps}, {channels}]")
         keep = taps - 1
     if keep:
         _need(state, "state", proj.dtype, 3)
@@ -902,9 +902,10 @@ def moe_route(h, router, token_request, ids, weights, top, softmax_scores=False,
 
 
 def moe_experts(h, gate_up, down, ids, weights, y, out, gate_max, up_min, up_max, alpha, up_shift, weight_on_input=True,
-                accumulate=False):
-    """The chosen experts of every row, each expert's matrices streamed once per row: gate_up [E, 2F, W] (gate rows,
-    then up rows), down [E, W, F]; y [N * top, F] scratch in h's type; out 32-bit [N, W], written or added to."""
+                accumulate=False, per_pair=None):
+    """The chosen experts of every row, an expert's matrices streamed once for every four rows that chose it:
+    gate_up [E, 2F, W] (gate rows, then up rows), down [E, W, F]; y [N * top, F] scratch in h's type and per_pair
+    [N * top, W] 32-bit scratch (made here when not given); out 32-bit [N, W], written or added to."""
     lib = _lib("moe", h, gate_up)
     _need(h, "h", _FLOATS, None, contiguous=False)
     N, W, ld = _rows_2d(h, "h")
@@ -919,12 +920,18 @@ def moe_experts(h, gate_up, down, ids, weights, y, out, gate_max, up_min, up_max
     if tuple(ids.shape) != (N, top) or tuple(weights.shape) != (N, top) or tuple(y.shape) != (N * top, F) \
             or tuple(out.shape) != (N, W):
         raise KernelError("ids, weights, y or out do not fit the rows and experts")
-    _check(lib.tnx_moe_experts(_p(h), c_int(ld), _p(gate_up), _p(down), _p(ids), _p(weights), _p(y), _p(out), c_int(N),
-                               c_int(W), c_int(F), c_int(top), c_float(gate_max), c_float(up_min), c_float(up_max),
+    if per_pair is None:
+        per_pair = torch.empty((N * top, W), dtype=torch.float32, device=h.device)
+    _need(per_pair, "per_pair", torch.float32, 2)
+    if tuple(per_pair.shape) != (N * top, W):
+        raise KernelError(f"per_pair must be [{N * top}, {W}]")
+    _check(lib.tnx_moe_experts(_p(h), c_int(ld), _p(gate_up), _p(down), _p(ids), _p(weights), _p(y), _p(per_pair), _p(out),
+                               c_int(N), c_int(W), c_int(F), c_int(top), c_int(E), c_float(gate_max), c_float(up_min),
+                               c_float(up_max),
                                c_float(alpha), c_float(up_shift), c_int(1 if weight_on_input else 0),
                                c_int(1 if accumulate else 0), c_int(_is_h16(h)), c_int(_is_h16(gate_up)), _stream()),
            "moe_experts")
-    add_launches(1)
+    add_launches(2)
 
 
 def moe_grouped_supported(h, gate_up, down) -> bool:

@@ -93,7 +93,8 @@ class ConvAttention(FusableMixer):
         f32 = lambda name: to_device(tensors[name], device, torch.float32) if name else None
         self.q_weight, self.k_weight = f32(s.q_norm), (f32(s.k_norm) if self.own_kv else None)
         if s.conv_taps:
-            self.conv_w = torch.cat([f32(name) for name, _ in self._conv_names()], dim=0).contiguous()
+            # [taps, channels]: the kernels read a tap's weights of consecutive channels together
+            self.conv_w = torch.cat([f32(name) for name, _ in self._conv_names()], dim=0).t().contiguous()
         if s.rotary is not None and s.rotary.dims:
             self.inv_freq = inverse_frequencies(s.rotary.dims, s.rotary.base, device, s.rotary.scaling)
             self.magnitude = rotation_magnitude(s.rotary.scaling)

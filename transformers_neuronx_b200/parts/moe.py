@@ -8,8 +8,9 @@
 
 The experts' matrices are kept stacked, [E, 2 ff, hidden] (gate rows, then up rows) and [E, hidden, ff], in the type
 they are stored in.  A step routes on the device (no read on the host: the part is graph-safe) and then takes one of
-two forms: few tokens stream the chosen experts' matrices once per token (csrc/moe.cu); many tokens are sorted by
-expert and run as grouped products on the tensor cores (csrc/moe_grouped.cu).
+two forms: in a 16-bit engine the (token, expert) pairs are sorted by expert and run as grouped products on the tensor
+cores (csrc/moe_grouped.cu, csrc/gemm_tc.cu); the 32-bit engine, and sizes the tensor-core product refuses, stream the
+chosen experts' matrices through the multiply-add units (csrc/moe.cu).
 """
 from __future__ import annotations
 
@@ -28,7 +29,10 @@ class RoutedExperts(FeedForward):
     graph_safe = True
     can_overwrite = True
     libraries = ("moe", "moe_grouped", "gemm_tc")
-    GROUPED_FROM = 64        # rows from which the grouped tensor-core form runs (16-bit engines)
+    # Rows from which the grouped tensor-core form runs in a 16-bit engine.  Measured at width 2048 (8 experts of inner
+    # width 2816, 2 a token): a decode step of 1 / 8 / 32 requests takes 0.48 / 0.75 / 1.03 ms with it and 0.52 / 1.10 /
+    # 2.54 ms with the kernels that stream the matrices through the multiply-add units, so it always runs.
+    GROUPED_FROM = 1
 
     def __init__(self, spec: RoutedFeedForwardSpec):
         s = self.spec = spec
@@ -87,7 +91,8 @@ class RoutedExperts(FeedForward):
             return
         y = ctx.scratch(N * s.top, s.ff)
         ops.moe_experts(h, self.gate_up, self.down, ids, weights, y, out, *limits, s.act_alpha, s.up_shift,
-                        weight_on_input=s.weight_on_input, accumulate=accumulate)
+                        weight_on_input=s.weight_on_input, accumulate=accumulate,
+                        per_pair=ctx.scratch(N * s.top, s.hidden, torch.float32))
 
 
 register_feed_forward("routed_experts", RoutedExperts)
