@@ -446,7 +446,9 @@ def test_the_entry_point_class_and_the_command_line(tmp_path):
 
 
 @pytest.mark.parametrize("N, W, E, top, F, on_input", [(300, 256, 8, 2, 128, True), (129, 320, 3, 3, 72, True),
-                                                      (1000, 64, 40, 1, 200, False), (64, 128, 5, 4, 64, True)])
+                                                      (1000, 64, 40, 1, 200, False), (64, 128, 5, 4, 64, True),
+                                                      (2, 2048, 8, 2, 2816, True), (9, 256, 8, 2, 136, True),      # tiles of 16
+                                                      (40, 512, 4, 1, 264, True), (70, 384, 6, 2, 1000, False)])   # of 32 and 64
 def test_experts_as_grouped_products_equal_the_streamed_form(N, W, E, top, F, on_input):
     """Many rows: the pairs sorted by expert into tiles of 128 rows and run on the tensor cores, against the form that
     streams an expert's matrices per row (which test_routing_and_experts holds against the plain implementation), with a

@@ -60,7 +60,7 @@ struct Params {
                                  // through distributed shared memory instead of scratch memory
     int sk_tiles;                // paired kernel: the last sk_tiles output tiles are shared out by K blocks
     int sk_pairs;                // ... over the first sk_pairs pairs
-    const int* group_of_tile;    // grouped product (normal form, 128 x 128 tiles): the group of every 128-token tile, -1: none;
+    const int* group_of_tile;    // grouped product: the group of every tile of tokens (128 of them, or BN in the swapped form), -1: none;
     int group_rows;              //   W holds group_rows rows per group, a tile of group g reads W's rows from g * group_rows on
 };
 
@@ -367,12 +367,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     // A grouped product: every tile of tokens belongs to one group (an expert) and multiplies that group's rows of W.
     // Which group is written by the kernel before this one, so it is read behind the dependency wait; a tile without
     // a group has nothing to do (nothing has been set up yet, so the whole CTA may leave).
-    int q_row0 = tile_q * BN;
-    if (!SWAP && p.group_of_tile != nullptr) {
+    // (In the swapped form the tokens are the Q operand; the CTAs of a cluster share their tile of tokens, so they leave together.)
+    int q_row0 = tile_q * BN, p_row0 = tile_p * TILE_P;
+    if (p.group_of_tile != nullptr) {
         pdl_wait();
-        const int g = p.group_of_tile[tile_p];
+        const int g = p.group_of_tile[SWAP ? tile_q : tile_p];
         if (g < 0) return;
-        q_row0 += g * p.group_rows;
+        if (SWAP) p_row0 += g * p.group_rows; else q_row0 += g * p.group_rows;
     }
     // Split K summed in a cluster, swapped form, 2, 4 or 8 splits: every CTA sends the bands of its partial tile
     // to their owners (one bulk copy from shared memory to shared memory each) and adds up what it receives
@@ -396,7 +397,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);
         uint8_t* a_dst = smem + (size_t)s * STAGE_BYTES;
         const int kx = (kb_begin + i) * BLOCK_K;
-        if (SWAP) tma_load_2d(a_dst, &map_p, &full_bar[s], kx, tile_p * TILE_P);
+        if (SWAP) tma_load_2d(a_dst, &map_p, &full_bar[s], kx, p_row0);
         else tma_load_2d(a_dst + A_BYTES, &map_q, &full_bar[s], kx, q_row0);
     };
     auto load_activations = [&](int i) {
@@ -1569,6 +1570,37 @@ TNX_EXPORT int tnx_gemm_tc_grouped(const void* A, const void* W, void* C, int M,
     CUtensorMap mp, mq;
     if (!make_map(&mp, A, M, K, lda, TILE_P) || !make_map(&mq, W, groups * N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
     return launch<128, 6, false>(mp, mq, p, dim3(M / TILE_P, (N + 127) / 128, 1), stream);
+}
+
+// The same for groups of few rows: the swapped form (the group's rows of W fill the 128-row operand, `bn` = 16, 32, 64 or
+// 128 tokens are the N of the MMA), group_of_tile per bn-row tile of A, M a multiple of bn.  K is split over the CTAs of a
+// cluster (2, 4 or 8) while that keeps the CTAs of the tiles that are expected to be used (`used_tiles`) within two an SM.
+TNX_EXPORT int tnx_gemm_tc_grouped_few(const void* A, const void* W, void* C, int M, int N, int K, int groups, int bn, int used_tiles,
+                                       int lda, int ldw, int ldc, int c_h16, const int* group_of_tile, int* err_word,
+                                       cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || groups <= 0) return 0;
+    if ((bn != 16 && bn != 32 && bn != 64 && bn != 128) || M % bn) return TNX_ERR_BAD_ARG;
+    if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || lda < K || ldw < K || ldc < N) return TNX_ERR_UNSUPPORTED;
+    if ((((uintptr_t)A | (uintptr_t)W) & 15) || (long long)groups * N >= (1ll << 31)) return TNX_ERR_UNSUPPORTED;
+    if (!err_word || !group_of_tile) return TNX_ERR_BAD_ARG;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int kb = (K + BLOCK_K - 1) / BLOCK_K, tiles_n = (N + TILE_P - 1) / TILE_P;
+    int splits = 1;
+    while (splits < MAX_CLUSTER && (long long)tiles_n * (used_tiles > 0 ? used_tiles : 1) * splits * 2 <= 2ll * sms && kb / (splits * 2) >= 4)
+        splits *= 2;
+    Params p{};
+    p.K = K; p.ldc = ldc; p.act = TNX_ACT_NONE; p.c_is_h16 = c_h16; p.C = C; p.err = err_word;
+    p.rows_p = N; p.rows_q = M; p.splits = splits; p.kb_per_split = (kb + splits - 1) / splits; p.cluster_reduce = splits > 1;
+    p.group_of_tile = group_of_tile; p.group_rows = N;
+    CUtensorMap mp, mq;
+    if (!make_map(&mp, W, groups * N, K, ldw, TILE_P) || !make_map(&mq, A, M, K, lda, bn)) return TNX_ERR_UNSUPPORTED;
+    dim3 grid(tiles_n, M / bn, splits);
+    if (bn == 16) return launch<16, 6, true>(mp, mq, p, grid, stream);
+    if (bn == 32) return launch<32, 5, true>(mp, mq, p, grid, stream);
+    if (bn == 64) return launch<64, 4, true>(mp, mq, p, grid, stream);
+    return launch<128, 3, true>(mp, mq, p, grid, stream);
 }
 
 // ---- a wait that runs out, for the tests of the error path --------------------------------------------

@@ -1,7 +1,7 @@
-// Routed experts for steps of many tokens: the (token, chosen expert) pairs are sorted by expert into a layout in which
-// every expert's rows begin at a multiple of 128, so that each 128-row tile belongs to one expert and the two products
-// of an expert run as grouped tensor-core products (gemm_tc.cu: tnx_gemm_tc_grouped).  The kernels of this file are what
-// lies around those products:
+// Routed experts on the tensor cores: the (token, chosen expert) pairs are sorted by expert into a layout in which every
+// expert's rows begin at a multiple of the tile (128 rows where experts get many rows; 16, 32 or 64 where they get few),
+// so that each tile belongs to one expert and the two products of an expert run as grouped tensor-core products
+// (gemm_tc.cu: tnx_gemm_tc_grouped, tnx_gemm_tc_grouped_few).  The kernels of this file are what lies around those products:
 //
 //   moe_plan_kernel      one block: counts per expert, every expert's first row, the expert of every tile (-1 beyond
 //                        the last used tile), and the row of every pair.  Which row of its expert's segment a pair
@@ -11,15 +11,14 @@
 //   moe_combine_kernel   out[token] (+)= sum over the token's pairs, in the order of the choice, of the down product's rows
 //
 // Nothing is read on the host: the sizes of the buffers follow from the numbers of tokens and experts alone (at most
-// pairs / 128 + experts tiles), so a step can be captured in a CUDA graph.
+// pairs / tile + experts tiles), so a step can be captured in a CUDA graph.
 #include "common.cuh"
 
 namespace {
-constexpr int TILE = 128;
 constexpr int MAX_EXPERTS = 1024;
 
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int n_experts, int max_tiles, int* __restrict__ group_of_tile,
+moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int n_experts, int max_tiles, int TILE, int* __restrict__ group_of_tile,
                 int* __restrict__ row_of_pair) {
     __shared__ int count[MAX_EXPERTS], first[MAX_EXPERTS], cursor[MAX_EXPERTS];
     pdl_launch_dependents();
@@ -75,7 +74,7 @@ moe_gather_kernel(const h16* __restrict__ h, int ld, const float* __restrict__ w
 }
 
 __global__ void __launch_bounds__(256)
-moe_act_kernel(const h16* __restrict__ gu, h16* __restrict__ y, const int* __restrict__ group_of_tile, int F,
+moe_act_kernel(const h16* __restrict__ gu, h16* __restrict__ y, const int* __restrict__ group_of_tile, int TILE, int F,
                float gate_max, float up_min, float up_max, float alpha, float up_shift) {
     pdl_launch_dependents();
     pdl_wait();
@@ -120,16 +119,17 @@ moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ row_o
 }  // namespace
 
 // The most tiles that n_pairs pairs spread over n_experts experts can take.
-TNX_EXPORT int tnx_moe_grouped_max_tiles(int n_pairs, int n_experts) {
-    return n_pairs / TILE + (n_pairs < n_experts ? n_pairs : n_experts);
+TNX_EXPORT int tnx_moe_grouped_max_tiles(int n_pairs, int n_experts, int tile) {
+    return n_pairs / tile + (n_pairs < n_experts ? n_pairs : n_experts);
 }
 
-TNX_EXPORT int tnx_moe_plan(const int* ids, int n_pairs, int n_experts, int max_tiles, int* group_of_tile, int* row_of_pair,
-                            cudaStream_t stream) {
+TNX_EXPORT int tnx_moe_plan(const int* ids, int n_pairs, int n_experts, int max_tiles, int tile, int* group_of_tile,
+                            int* row_of_pair, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
-    if (n_experts <= 0 || n_experts > MAX_EXPERTS || max_tiles < tnx_moe_grouped_max_tiles(n_pairs, n_experts)) return TNX_ERR_BAD_ARG;
-    return tnx_launch_in_order(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, n_pairs, n_experts, max_tiles, group_of_tile,
-                               row_of_pair);
+    if (n_experts <= 0 || n_experts > MAX_EXPERTS || tile <= 0 || max_tiles < tnx_moe_grouped_max_tiles(n_pairs, n_experts, tile))
+        return TNX_ERR_BAD_ARG;
+    return tnx_launch_in_order(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, n_pairs, n_experts, max_tiles, tile,
+                               group_of_tile, row_of_pair);
 }
 
 TNX_EXPORT int tnx_moe_gather(const void* h, int ld, const float* weights, const int* row_of_pair, void* x, int n_pairs, int W,
@@ -139,11 +139,11 @@ TNX_EXPORT int tnx_moe_gather(const void* h, int ld, const float* weights, const
                                (h16*)x, W, top, weight_on_input);
 }
 
-TNX_EXPORT int tnx_moe_act(const void* gu, void* y, const int* group_of_tile, int rows, int F, float gate_max, float up_min,
-                           float up_max, float alpha, float up_shift, cudaStream_t stream) {
+TNX_EXPORT int tnx_moe_act(const void* gu, void* y, const int* group_of_tile, int tile, int rows, int F, float gate_max,
+                           float up_min, float up_max, float alpha, float up_shift, cudaStream_t stream) {
     if (rows <= 0) return 0;
     return tnx_launch_in_order(moe_act_kernel, dim3(rows), dim3(F >= 512 ? 256 : 128), 0, stream, (const h16*)gu, (h16*)y,
-                               group_of_tile, F, gate_max, up_min, up_max, alpha, up_shift);
+                               group_of_tile, tile, F, gate_max, up_min, up_max, alpha, up_shift);
 }
 
 TNX_EXPORT int tnx_moe_combine(const float* rows, const int* row_of_pair, const float* weights, float* out, int N, int W, int top,

@@ -944,17 +944,24 @@ def moe_grouped_supported(h, gate_up, down) -> bool:
             and gate_up.data_ptr() % 16 == 0 and down.data_ptr() % 16 == 0 and E * max(F2, W) < 2 ** 31)
 
 
-def gemm_tc_grouped(a, w, out, group_of_tile):
-    """out[m] = a[m] @ w[g]^T for the rows m of every 128-row tile, g = group_of_tile[m // 128] (-1: the tile is
-    skipped).  a [M, K] (M a multiple of 128) and w [groups, N, K] in one 16-bit type; out [M, N] in that type or 32-bit."""
+def gemm_tc_grouped(a, w, out, group_of_tile, tile=128, used_tiles=0):
+    """out[m] = a[m] @ w[g]^T for the rows m of every tile of `tile` rows, g = group_of_tile[m // tile] (-1: the tile is
+    skipped).  a [M, K] (M a multiple of tile) and w [groups, N, K] in one 16-bit type; out [M, N] in that type or
+    32-bit.  tile 128: tiles of 128 tokens x 128 features; 16, 32 or 64: the swapped form (the group's matrix fills the
+    128-row operand), K split in clusters while the `used_tiles` tiles expected to have a group leave SMs idle."""
     lib = _lib("gemm_tc", a, w, out)
     _need(a, "a", _H16, 2); _need(w, "w", a.dtype, 3); _need(out, "out", _FLOATS, 2)
     _need(group_of_tile, "group_of_tile", torch.int32, 1)
     M, K = a.shape
     G, N, Kw = w.shape
-    if Kw != K or tuple(out.shape) != (M, N) or M % 128 or group_of_tile.shape[0] < M // 128:
+    if Kw != K or tuple(out.shape) != (M, N) or tile not in (16, 32, 64, 128) or M % tile or group_of_tile.shape[0] < M // tile:
         raise KernelError(f"grouped product shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     st = _state(a.device)
+    if tile < 128:
+        _check(lib.tnx_gemm_tc_grouped_few(_p(a), _p(w), _p(out), c_int(M), c_int(N), c_int(K), c_int(G), c_int(tile),
+                                           c_int(int(used_tiles)), c_int(K), c_int(K), c_int(N), c_int(_is_h16(out)),
+                                           _p(group_of_tile), _p(st["err"]), _stream()), "gemm_tc_grouped")
+        return
     _check(lib.tnx_gemm_tc_grouped(_p(a), _p(w), _p(out), c_int(M), c_int(N), c_int(K), c_int(G), c_int(K), c_int(K), c_int(N),
                                    c_int(_is_h16(out)), _p(group_of_tile), _p(st["err"]), _stream()), "gemm_tc_grouped")
 
@@ -971,32 +978,36 @@ def moe_grouped(ctx, h, gate_up, down, ids, weights, out, gate_max, up_min, up_m
     E, F2, _ = gate_up.shape
     F, top = F2 // 2, ids.shape[1]
     P = N * top
-    tiles = lib.tnx_moe_grouped_max_tiles(c_int(P), c_int(E))
-    rows = tiles * 128
+    # the tile: the smallest that holds twice an expert's even share of the pairs (so that most experts take one tile and
+    # their matrices are streamed once), 128 rows where the experts get many
+    tile = next((t for t in (16, 32, 64) if 2 * P <= t * E), 128)
+    tiles = lib.tnx_moe_grouped_max_tiles(c_int(P), c_int(E), c_int(tile))
+    used = min(E, P) + P // tile // 2
+    rows = tiles * tile
     group_of_tile = ctx.scratch(1, tiles, torch.int32).view(-1)
     row_of_pair = ctx.scratch(1, P, torch.int32).view(-1)
     x = ctx.scratch(rows, W, h.dtype)
-    moe_sort_rows(lib, h, ids, weights, E, tiles, group_of_tile, row_of_pair, x, weight_on_input)
+    moe_sort_rows(lib, h, ids, weights, E, tiles, tile, group_of_tile, row_of_pair, x, weight_on_input)
     gu = ctx.scratch(rows, F2, h.dtype)
-    gemm_tc_grouped(x, gate_up, gu, group_of_tile)
+    gemm_tc_grouped(x, gate_up, gu, group_of_tile, tile, used)
     y = ctx.scratch(rows, F, h.dtype)
-    moe_activation(lib, gu, y, group_of_tile, gate_max, up_min, up_max, alpha, up_shift)
+    moe_activation(lib, gu, y, group_of_tile, tile, gate_max, up_min, up_max, alpha, up_shift)
     per_pair = ctx.scratch(rows, W, torch.float32)
-    gemm_tc_grouped(y, down, per_pair, group_of_tile)
+    gemm_tc_grouped(y, down, per_pair, group_of_tile, tile, used)
     moe_combine(lib, per_pair, row_of_pair, weights, out, accumulate, weight_on_input)
 
 
-def moe_sort_rows(lib, h, ids, weights, n_experts, tiles, group_of_tile, row_of_pair, x, weight_on_input):
+def moe_sort_rows(lib, h, ids, weights, n_experts, tiles, tile, group_of_tile, row_of_pair, x, weight_on_input):
     """The plan (every pair's row, every tile's expert) and the rows themselves, x[row(pair)] = weight * h[token]."""
     P, top = ids.numel(), ids.shape[1]
-    _check(lib.tnx_moe_plan(_p(ids), c_int(P), c_int(n_experts), c_int(tiles), _p(group_of_tile), _p(row_of_pair), _stream()),
-           "moe_plan")
+    _check(lib.tnx_moe_plan(_p(ids), c_int(P), c_int(n_experts), c_int(tiles), c_int(tile), _p(group_of_tile), _p(row_of_pair),
+                            _stream()), "moe_plan")
     _check(lib.tnx_moe_gather(_p(h), c_int(h.stride(0)), _p(weights), _p(row_of_pair), _p(x), c_int(P), c_int(h.shape[1]),
                               c_int(top), c_int(1 if weight_on_input else 0), _stream()), "moe_gather")
 
 
-def moe_activation(lib, gu, y, group_of_tile, gate_max, up_min, up_max, alpha, up_shift):
-    _check(lib.tnx_moe_act(_p(gu), _p(y), _p(group_of_tile), c_int(gu.shape[0]), c_int(y.shape[1]), c_float(gate_max),
+def moe_activation(lib, gu, y, group_of_tile, tile, gate_max, up_min, up_max, alpha, up_shift):
+    _check(lib.tnx_moe_act(_p(gu), _p(y), _p(group_of_tile), c_int(tile), c_int(gu.shape[0]), c_int(y.shape[1]), c_float(gate_max),
                            c_float(up_min), c_float(up_max), c_float(alpha), c_float(up_shift), _stream()), "moe_act")
 
 
