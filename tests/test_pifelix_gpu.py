@@ -193,6 +193,7 @@ def test_the_chunked_mask_in_every_attention_kernel(chunk, n_heads, n_kv, d):
     (100, 7, 7, 30, torch.float32, False, False, True),
     (256, 8, 1, 128, torch.bfloat16, False, False, True),
     (64, 40, 8, 24, torch.float32, True, True, False),        # what other designs do: softmax, renormalised, on the output
+    (48, 20, 16, 16, torch.float32, False, False, True),
     (320, 3, 2, 50, torch.bfloat16, False, False, True),
 ])
 def test_routing_and_experts(W, E, top, F, dtype, softmax, renorm, on_input):

@@ -19,35 +19,51 @@
 #include "common.cuh"
 
 namespace {
-constexpr int MAX_TOP = 8;
+constexpr int MAX_TOP = 16;
 constexpr int MAX_EXPERTS = 1024;
 
-template <typename TW> __device__ __forceinline__ float dot8(const TW* w, const float* x);
-template <> __device__ __forceinline__ float dot8<h16>(const h16* w, const float* x) {
-    const uint4 raw = *(const uint4*)w;
-    const h16x2* h = (const h16x2*)&raw;
-    float s = 0.f;
+// 8 elements of a matrix as they are loaded (converted when they are used, so that several loads can be in flight).
+template <typename TW> struct Raw8;
+template <> struct Raw8<h16> {
+    uint4 raw;
+    __device__ __forceinline__ void load(const h16* p) { raw = *(const uint4*)p; }
+    __device__ __forceinline__ void get(float (&v)[8]) const {
+        const h16x2* h = (const h16x2*)&raw;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = h16x2_to_float2(h[i]);
-        s = fmaf(f.x, x[2 * i], s);
-        s = fmaf(f.y, x[2 * i + 1], s);
+        for (int i = 0; i < 4; ++i) { const float2 f = h16x2_to_float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
     }
-    return s;
-}
-template <> __device__ __forceinline__ float dot8<float>(const float* w, const float* x) {
-    const float4 a = *(const float4*)w, b = *(const float4*)(w + 4);
-    float s = 0.f;
-    s = fmaf(a.x, x[0], s); s = fmaf(a.y, x[1], s); s = fmaf(a.z, x[2], s); s = fmaf(a.w, x[3], s);
-    s = fmaf(b.x, x[4], s); s = fmaf(b.y, x[5], s); s = fmaf(b.z, x[6], s); s = fmaf(b.w, x[7], s);
-    return s;
-}
-// <w, x> over K elements by one warp; every lane gets the sum.  The order of the additions depends on K alone.
+    static constexpr int AHEAD = 4;
+};
+template <> struct Raw8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) { a = *(const float4*)p; b = *(const float4*)(p + 4); }
+    __device__ __forceinline__ void get(float (&v)[8]) const {
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static constexpr int AHEAD = 2;
+};
+
+// <w, x> over K elements by one warp; every lane gets the sum.  The order of the additions depends on K alone.  A lane
+// asks for AHEAD pieces of 16 bytes before it uses the first.
 template <typename TW>
 __device__ __forceinline__ float warp_dot(const TW* __restrict__ w, const float* x, int K, int lane, bool vec) {
+    constexpr int U = Raw8<TW>::AHEAD;
     float s = 0.f;
     if (vec) {
-        for (int c = lane * 8; c < K; c += 256) s += dot8<TW>(w + c, x + c);
+        for (int c = lane * 8; c < K; c += 256 * U) {
+            Raw8<TW> a[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) if (c + 256 * u < K) a[u].load(w + c + 256 * u);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (c + 256 * u < K) {
+                    float af[8];
+                    a[u].get(af);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) s = fmaf(af[i], x[c + 256 * u + i], s);
+                }
+            }
+        }
     } else {
         for (int c = lane; c < K; c += 32) s = fmaf(to_float(w[c]), x[c], s);
     }
@@ -164,27 +180,6 @@ template <> struct Load8<float> {
 };
 
 constexpr int MT = 4;          // rows of one expert that share one pass over its matrices
-
-// 8 elements of a matrix as they are loaded (converted when they are used, so that several loads can be in flight).
-template <typename TW> struct Raw8;
-template <> struct Raw8<h16> {
-    uint4 raw;
-    __device__ __forceinline__ void load(const h16* p) { raw = *(const uint4*)p; }
-    __device__ __forceinline__ void get(float (&v)[8]) const {
-        const h16x2* h = (const h16x2*)&raw;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { const float2 f = h16x2_to_float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
-    }
-    static constexpr int AHEAD = 4;
-};
-template <> struct Raw8<float> {
-    float4 a, b;
-    __device__ __forceinline__ void load(const float* p) { a = *(const float4*)p; b = *(const float4*)(p + 4); }
-    __device__ __forceinline__ void get(float (&v)[8]) const {
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    }
-    static constexpr int AHEAD = 2;
-};
 
 // One pass over the rows `w0` and (when given) `w1` of length K for up to MT staged rows xs[r][K]: acc0[r] = <w0, xs[r]>.
 // A lane asks for AHEAD pieces of 16 bytes of every row before it uses the first: with a row or two of tokens the
@@ -355,7 +350,7 @@ moe_sum_kernel(const float* __restrict__ per_pair, const int* __restrict__ ids, 
     pdl_wait();
     const int n = blockIdx.x;
     if (ids[(size_t)n * top] < 0) return;                   // a padded row of a captured step
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
         float s = 0.f;
         for (int j = 0; j < top; ++j) {
             const float v = per_pair[((size_t)n * top + j) * W + c];
@@ -414,7 +409,7 @@ TNX_EXPORT int tnx_moe_experts(const void* h, int ld, const void* gate_up, const
         rc = tnx_launch_in_order(moe_down_kernel<T, TW>, g2, dim3(128), smem2, stream, (const T*)y, (const TW*)down,    \
                                  ids, per_pair, W, F, pairs, per2);                                                     \
         if (rc != 0) return rc;                                                                                         \
-        return tnx_launch_in_order(moe_sum_kernel, dim3(N), dim3(128), 0, stream, (const float*)per_pair, ids, weights, \
+        return tnx_launch_in_order(moe_sum_kernel, dim3(N, N >= 256 ? 1 : (W + 511) / 512), dim3(128), 0, stream, (const float*)per_pair, ids, weights, \
                                    out, W, top, accumulate, weight_on_input);                                           \
     } while (0)
     if (h_h16 && w_h16) GO(h16, h16);

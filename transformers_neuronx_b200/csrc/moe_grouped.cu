@@ -106,7 +106,7 @@ moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ row_o
     pdl_wait();
     const int n = blockIdx.x;
     if (row_of_pair[(size_t)n * top] < 0) return;                 // a padded row of a captured step
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
         float s = 0.f;
         for (int j = 0; j < top; ++j) {
             const float v = rows[(size_t)row_of_pair[(size_t)n * top + j] * W + c];
@@ -149,6 +149,7 @@ TNX_EXPORT int tnx_moe_act(const void* gu, void* y, const int* group_of_tile, in
 TNX_EXPORT int tnx_moe_combine(const float* rows, const int* row_of_pair, const float* weights, float* out, int N, int W, int top,
                                int accumulate, int weight_on_input, cudaStream_t stream) {
     if (N <= 0) return 0;
-    return tnx_launch_in_order(moe_combine_kernel, dim3(N), dim3(128), 0, stream, rows, row_of_pair, weights, out, W, top,
+    // few tokens: a slice of the width a block, so that the loads of a row are asked for together
+    return tnx_launch_in_order(moe_combine_kernel, dim3(N, N >= 256 ? 1 : (W + 511) / 512), dim3(128), 0, stream, rows, row_of_pair, weights, out, W, top,
                                accumulate, weight_on_input);
 }

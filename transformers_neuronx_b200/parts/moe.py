@@ -38,8 +38,8 @@ class RoutedExperts(FeedForward):
         s = self.spec = spec
         if not (1 <= s.top <= s.n_experts) or len(s.experts) != s.n_experts:
             raise ValueError(f"{s.top} of {s.n_experts} experts ({len(s.experts)} listed) is not a choice")
-        if s.top > 8 or s.n_experts > 1024:
-            raise ValueError("the routing kernel takes up to 8 chosen of up to 1024 experts")
+        if s.top > 16 or s.n_experts > 1024:
+            raise ValueError("the routing kernel takes up to 16 chosen of up to 1024 experts")
         if s.scores not in ("sigmoid", "softmax"):
             raise ValueError(f"unknown scores {s.scores!r}: sigmoid or softmax")
         self.router = self.gate_up = self.down = None
