@@ -199,6 +199,16 @@ __global__ void __launch_bounds__(128) conv_norm_rotate_vec_kernel(const ConvPre
     const int n = blockIdx.x, lane = threadIdx.x & 31;
     const int req = p.token_request[n];
     if (req < 0) return;                                    // a padded row of a captured step
+    const int pos = p.positions[n];
+    // the token's sines and cosines once for all heads of the block (they were a third of the kernel's instructions when
+    // every lane computed its own four)
+    __shared__ float2 turn[32 * MAX_R];
+    for (int i = threadIdx.x; 2 * i < p.rot_dims; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * p.inv_freq[i], &sn, &cs);
+        turn[i] = make_float2(cs * p.magnitude, sn * p.magnitude);
+    }
+    __syncthreads();
     const int Lk = p.dk >> 3, Lv = p.dv >> 3;
     const int per_k = 32 / Lk, per_v = Lv ? 32 / Lv : 1, n_qk = p.H + p.G;
     const int warps_qk = (n_qk + per_k - 1) / per_k, warps_v = p.G ? (p.G + per_v - 1) / per_v : 0;
@@ -209,7 +219,7 @@ __global__ void __launch_bounds__(128) conv_norm_rotate_vec_kernel(const ConvPre
     const int unit = (values ? (w - warps_qk) * per_v : w * per_k) + lane / L, piece = lane % L;
     const bool active = lane < (32 / L) * L && unit < (values ? p.G : n_qk);
     const int ch = (values ? n_qk * p.dk + unit * p.dv : unit * p.dk) + piece * 8;
-    const int pos = p.positions[n], idx = n - p.q_start[req], slot = p.state_slots[req];
+    const int idx = n - p.q_start[req], slot = p.state_slots[req];
     constexpr int KEEP = TAPS - 1;
     float y[8];
 #pragma unroll
@@ -251,9 +261,14 @@ __global__ void __launch_bounds__(128) conv_norm_rotate_vec_kernel(const ConvPre
         float ssq = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) ssq = fmaf(y[i], y[i], ssq);
-        const int seg = (lane / L) * L;
         float total = 0.f;
-        for (int o = 0; o < L; ++o) total += __shfl_sync(0xffffffffu, ssq, (seg + o) & 31);
+        if ((L & (L - 1)) == 0) {                           // the head's lanes are an aligned power of two: a butterfly
+            total = ssq;
+            for (int o = L >> 1; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        } else {
+            const int seg = (lane / L) * L;
+            for (int o = 0; o < L; ++o) total += __shfl_sync(0xffffffffu, ssq, (seg + o) & 31);
+        }
         if (active && g != nullptr) {
             const float rinv = 1.0f / sqrtf(total / (float)dims + p.eps);
 #pragma unroll
@@ -264,12 +279,10 @@ __global__ void __launch_bounds__(128) conv_norm_rotate_vec_kernel(const ConvPre
             for (int t = 0; t < 4; ++t) {
                 const int c = piece * 8 + 2 * t;
                 if (c + 1 < p.rot_dims) {
-                    float sn, cs;
-                    sincosf((float)pos * p.inv_freq[c >> 1], &sn, &cs);
-                    sn *= p.magnitude; cs *= p.magnitude;
+                    const float2 cs_sn = turn[c >> 1];
                     const float a = y[2 * t], b = y[2 * t + 1];
-                    y[2 * t] = a * cs - b * sn;
-                    y[2 * t + 1] = b * cs + a * sn;
+                    y[2 * t] = a * cs_sn.x - b * cs_sn.y;
+                    y[2 * t + 1] = b * cs_sn.x + a * cs_sn.y;
                 }
             }
         }
