@@ -1592,7 +1592,11 @@ TNX_EXPORT int tnx_gemm_tc_grouped_few(const void* A, const void* W, void* C, in
     if (!err_word || !group_of_tile) return TNX_ERR_BAD_ARG;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    static int cached_sms[64] = {0};
+    if (dev >= 0 && dev < 64) {
+        if (!cached_sms[dev]) cudaDeviceGetAttribute(&cached_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+        sms = cached_sms[dev];
+    }
     const int kb = (K + BLOCK_K - 1) / BLOCK_K, tiles_n = (N + TILE_P - 1) / TILE_P;
     int splits = 1;
     while (splits < MAX_CLUSTER && (long long)tiles_n * (used_tiles > 0 ? used_tiles : 1) * splits * 2 <= 2ll * sms && kb / (splits * 2) >= 4)
