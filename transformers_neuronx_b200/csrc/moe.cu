@@ -14,8 +14,8 @@
 //   moe_down_kernel        a block per (expert, slice of the width): the same for the down product, one 32-bit row per pair
 //   moe_sum_kernel         adds a token's pairs up in the order of the choice and writes or adds the 32-bit result
 // They stream a chosen expert's matrices once for every four tokens that chose it, through the multiply-add units: the
-// form for steps of few tokens (and of the 32-bit engine).  Steps of many tokens take the grouped tensor-core products of
-// moe_grouped.cu.
+// form of the 32-bit engine and of sizes the tensor-core product refuses.  A 16-bit engine takes the grouped tensor-core
+// products of moe_grouped.cu at every number of tokens (and this file's router).
 #include "common.cuh"
 
 namespace {
